@@ -1,0 +1,102 @@
+"""ctypes binding of ``include/mamba_b200.h`` (the same declarations a Rust
+``extern "C"`` block would carry)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(HERE, "libmamba_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def lib_path() -> str:
+    return _LIB
+
+
+class SscanFwdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("T", C.c_int), ("D", C.c_int), ("N", C.c_int),
+        ("x", C.c_void_p), ("ld_x", C.c_longlong),
+        ("delta", C.c_void_p), ("ld_delta", C.c_longlong), ("delta_softplus", C.c_int),
+        ("Bm", C.c_void_p), ("Cm", C.c_void_p), ("ld_bc", C.c_longlong),
+        ("z", C.c_void_p), ("ld_z", C.c_longlong), ("z_mode", C.c_int),
+        ("a_neg", C.c_void_p), ("Dp", C.c_void_p),
+        ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("conv_state", C.c_void_p), ("K", C.c_int),
+        ("ssm_state", C.c_void_p),
+        ("y", C.c_void_p), ("ld_y", C.c_longlong),
+        ("u_out", C.c_void_p), ("ld_u", C.c_longlong),
+        ("chunk_states", C.c_void_p), ("save_stride", C.c_int),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the library; raises LibraryMissing (never falls back) if absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB):
+            raise LibraryMissing(
+                f"{_LIB} not found: build it with `python -m mamba_rs_b200.build` "
+                "(nvcc, sm_100a). There is no CPU fallback.")
+        _lib = C.CDLL(_LIB)
+        _lib.mamba_b200_last_error.restype = C.c_char_p
+        _lib.mamba_b200_last_error.argtypes = [C.c_void_p]
+        _lib.mamba_b200_init.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+        _lib.mamba_b200_destroy.argtypes = [C.c_void_p]
+        _lib.mamba_b200_check_status.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.mamba_b200_sscan_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanFwdArgs)]
+    return _lib
+
+
+class Handle:
+    """Per-device library handle (mamba_b200_init / mamba_b200_destroy)."""
+
+    def __init__(self, device: int = 0):
+        self._h = C.c_void_p()
+        self.device = device
+        rc = lib().mamba_b200_init(device, C.byref(self._h))
+        if rc != 0:
+            msg = lib().mamba_b200_last_error(self._h).decode() if self._h else "no handle"
+            if self._h:
+                lib().mamba_b200_destroy(self._h)
+                self._h = C.c_void_p()
+            raise RuntimeError(f"mamba_b200_init({device}) failed ({rc}): {msg}")
+
+    @property
+    def ptr(self):
+        return self._h
+
+    def check(self, rc: int, what: str):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed ({rc}): {lib().mamba_b200_last_error(self._h).decode()}")
+
+    def check_status(self, stream=None):
+        self.check(lib().mamba_b200_check_status(self._h, C.c_void_p(stream or 0)), "check_status")
+
+    def close(self):
+        if self._h:
+            lib().mamba_b200_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_handles = {}
+
+
+def default_handle(device: int) -> Handle:
+    if device not in _handles:
+        _handles[device] = Handle(device)
+    return _handles[device]

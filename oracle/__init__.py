@@ -1,0 +1,280 @@
+"""ctypes front-end of the CPU oracle (``liboracle.so``).
+
+Test infrastructure only: imported by ``tests/``, by the smoke check and by the
+CPU-baseline / reference legs of ``bench.py``; the product package never
+imports it.  All arrays are C-contiguous numpy ``float32`` (``float64`` for the
+shadow).  See ``m1_oracle.c`` / ``m3_oracle.c`` for the reference citations.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile ``liboracle.so`` with the committed Makefile (gcc only)."""
+    srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.endswith(".c")]
+    stale = (not os.path.exists(_LIB_PATH)) or any(
+        os.path.getmtime(s) > os.path.getmtime(_LIB_PATH) for s in srcs
+    )
+    if force or stale:
+        subprocess.check_call(["make", "-C", _HERE, "-B", "liboracle.so"],
+                              stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.orc_fast_exp_scalar.restype = C.c_float
+        _lib.orc_fast_exp_scalar.argtypes = [C.c_float]
+        _lib.orc_fast_exp_simd_lane.restype = C.c_float
+        _lib.orc_fast_exp_simd_lane.argtypes = [C.c_float]
+        _lib.orc_m1_layer_floats.restype = C.c_long
+        _lib.orc_m1_weights_floats.restype = C.c_long
+    return _lib
+
+
+class M1Shape(C.Structure):
+    _fields_ = [("B", C.c_int), ("T", C.c_int), ("D", C.c_int), ("N", C.c_int),
+                ("K", C.c_int), ("ld_x", C.c_long), ("ld_delta", C.c_long),
+                ("ld_z", C.c_long), ("ld_bc", C.c_long), ("ld_y", C.c_long),
+                ("delta_softplus", C.c_int), ("has_z", C.c_int)]
+
+
+class M1Config(C.Structure):
+    _fields_ = [("d_model", C.c_int), ("n_layers", C.c_int), ("d_state", C.c_int),
+                ("d_conv", C.c_int), ("expand", C.c_int), ("dt_rank", C.c_int),
+                ("input_dim", C.c_int)]
+
+    @property
+    def d_inner(self):
+        return self.expand * self.d_model
+
+    @property
+    def xdbl_dim(self):
+        return self.dt_rank + 2 * self.d_state
+
+
+def _p(a, dtype=np.float32):
+    if a is None:
+        return None
+    assert a.dtype == dtype and a.flags["C_CONTIGUOUS"], (a.dtype, a.flags)
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def fast_exp(x, simd: bool = False) -> np.ndarray:
+    x = np.atleast_1d(np.asarray(x, dtype=np.float32))
+    f = lib().orc_fast_exp_simd_lane if simd else lib().orc_fast_exp_scalar
+    return np.array([f(float(v)) for v in x.ravel()], dtype=np.float32).reshape(x.shape)
+
+
+def fast_exp_inplace(buf: np.ndarray) -> np.ndarray:
+    buf = np.ascontiguousarray(buf, dtype=np.float32).copy()
+    lib().orc_fast_exp_inplace(_p(buf), C.c_long(buf.size))
+    return buf
+
+
+def _shape(x, delta, Bm, z, N, K, delta_softplus):
+    B, T, D = delta.shape
+    return M1Shape(B, T, D, N, K, x.shape[-1], delta.shape[-1],
+                   z.shape[-1] if z is not None else 0, Bm.shape[-1], D,
+                   int(delta_softplus), int(z is not None))
+
+
+def m1_fused_fwd(x, delta, Bm, Cm, z, a_neg, Dp, conv_w=None, conv_b=None,
+                 conv_state=None, ssm_state=None, delta_softplus=True,
+                 want_u=False, want_h=False):
+    """Fused forward.  x/delta/z: [B,T,D]; Bm/Cm: [B,T,N]; a_neg [D,N]; Dp [D];
+    conv_w [D,K], conv_b [D], conv_state [B,D,K], ssm_state [B,D,N] (copied).
+    Returns dict(y, ssm_state, conv_state, u, delta, h_all)."""
+    x, delta, Bm, Cm, z = map(_f32, (x, delta, Bm, Cm, z))
+    a_neg, Dp, conv_w, conv_b = map(_f32, (a_neg, Dp, conv_w, conv_b))
+    B, T, D = delta.shape
+    N = a_neg.shape[1]
+    K = 0 if conv_w is None else conv_w.shape[1]
+    s = _shape(x, delta, Bm, z, N, K, delta_softplus)
+    ssm = np.zeros((B, D, N), np.float32) if ssm_state is None else _f32(ssm_state).copy()
+    cst = None
+    if K:
+        cst = np.zeros((B, D, K), np.float32) if conv_state is None else _f32(conv_state).copy()
+    y = np.empty((B, T, D), np.float32)
+    u = np.empty((B, T, D), np.float32) if want_u else None
+    dl = np.empty((B, T, D), np.float32) if want_u else None
+    h_all = np.empty((B, T + 1, D, N), np.float32) if want_h else None
+    lib().orc_m1_fused_fwd(C.byref(s), _p(x), _p(delta), _p(Bm), _p(Cm), _p(z), _p(a_neg),
+                           _p(Dp), _p(conv_w), _p(conv_b), _p(cst), _p(ssm), _p(y), _p(u),
+                           _p(dl), _p(h_all))
+    return dict(y=y, ssm_state=ssm, conv_state=cst, u=u, delta=dl, h_all=h_all)
+
+
+def m1_fused_fwd_f64(x, delta, Bm, Cm, z, a_neg, Dp, conv_w=None, conv_b=None,
+                     conv_state=None, ssm_state=None, delta_softplus=True):
+    f64 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float64)
+    x, delta, Bm, Cm, z, a_neg, Dp, conv_w, conv_b = map(
+        f64, (x, delta, Bm, Cm, z, a_neg, Dp, conv_w, conv_b))
+    B, T, D = delta.shape
+    N = a_neg.shape[1]
+    K = 0 if conv_w is None else conv_w.shape[1]
+    s = _shape(x, delta, Bm, z, N, K, delta_softplus)
+    ssm = np.zeros((B, D, N)) if ssm_state is None else f64(ssm_state).copy()
+    cst = None
+    if K:
+        cst = np.zeros((B, D, K)) if conv_state is None else f64(conv_state).copy()
+    y = np.empty((B, T, D))
+    d = np.float64
+    lib().orc_m1_fused_fwd_f64(C.byref(s), _p(x, d), _p(delta, d), _p(Bm, d), _p(Cm, d),
+                               _p(z, d), _p(a_neg, d), _p(Dp, d), _p(conv_w, d),
+                               _p(conv_b, d), _p(cst, d), _p(ssm, d), _p(y, d))
+    return dict(y=y, ssm_state=ssm, conv_state=cst)
+
+
+def m1_fused_bwd(x, delta, Bm, Cm, z, a_neg, Dp, dg, conv_w=None, conv_b=None,
+                 conv_state0=None, ssm_state0=None, delta_softplus=True, d_u_extra=None):
+    """Fused backward.  Returns dict(d_x, d_delta, d_z, dB, dC, dA_log, dD,
+    dconv_w, dconv_b); parameter gradients start from zero."""
+    x, delta, Bm, Cm, z, dg = map(_f32, (x, delta, Bm, Cm, z, dg))
+    a_neg, Dp, conv_w, conv_b = map(_f32, (a_neg, Dp, conv_w, conv_b))
+    conv_state0, ssm_state0, d_u_extra = map(_f32, (conv_state0, ssm_state0, d_u_extra))
+    B, T, D = delta.shape
+    N = a_neg.shape[1]
+    K = 0 if conv_w is None else conv_w.shape[1]
+    s = _shape(x, delta, Bm, z, N, K, delta_softplus)
+    d_x = np.zeros((B, T, D), np.float32)
+    d_delta = np.zeros((B, T, D), np.float32)
+    d_z = np.zeros((B, T, D), np.float32)
+    dB = np.zeros((B, T, N), np.float32)
+    dC = np.zeros((B, T, N), np.float32)
+    dA = np.zeros((D, N), np.float32)
+    dD = np.zeros((D,), np.float32)
+    dcw = np.zeros((D, max(K, 1)), np.float32)
+    dcb = np.zeros((D,), np.float32)
+    lib().orc_m1_fused_bwd(C.byref(s), _p(x), _p(delta), _p(Bm), _p(Cm), _p(z), _p(a_neg),
+                           _p(Dp), _p(conv_w), _p(conv_b), _p(conv_state0), _p(ssm_state0),
+                           _p(dg), _p(d_u_extra), _p(d_x), _p(d_delta), _p(d_z), _p(dB),
+                           _p(dC), _p(dA), _p(dD), _p(dcw), _p(dcb))
+    return dict(d_x=d_x, d_delta=d_delta, d_z=d_z, dB=dB, dC=dC, dA_log=dA, dD=dD,
+                dconv_w=dcw[:, :K] if K else None, dconv_b=dcb if K else None)
+
+
+def m1_step(x, delta, Bm, Cm, z, a_neg, Dp, conv_w=None, conv_b=None, conv_state=None,
+            ssm_state=None, delta_softplus=True):
+    """T=1 decode step.  x/delta/z: [B,D]; Bm/Cm: [B,N]."""
+    x, delta, Bm, Cm, z = map(_f32, (x, delta, Bm, Cm, z))
+    a_neg, Dp, conv_w, conv_b = map(_f32, (a_neg, Dp, conv_w, conv_b))
+    B, D = delta.shape
+    N = a_neg.shape[1]
+    K = 0 if conv_w is None else conv_w.shape[1]
+    s = M1Shape(B, 1, D, N, K, x.shape[-1], D, D if z is not None else 0, Bm.shape[-1], D,
+                int(delta_softplus), int(z is not None))
+    ssm = _f32(ssm_state).copy()
+    cst = _f32(conv_state).copy() if K else None
+    y = np.empty((B, D), np.float32)
+    lib().orc_m1_step(C.byref(s), _p(x), _p(delta), _p(Bm), _p(Cm), _p(z), _p(a_neg), _p(Dp),
+                      _p(conv_w), _p(conv_b), _p(cst), _p(ssm), _p(y))
+    return dict(y=y, ssm_state=ssm, conv_state=cst)
+
+
+# -- full backbone (BASELINE config #1) ------------------------------------
+
+def m1_config(d_model=128, n_layers=2, d_state=16, d_conv=4, expand=2, dt_rank=None,
+              input_dim=None) -> M1Config:
+    dt_rank = dt_rank if dt_rank is not None else (d_model + 15) // 16
+    return M1Config(d_model, n_layers, d_state, d_conv, expand, dt_rank,
+                    input_dim if input_dim is not None else d_model)
+
+
+def m1_weights_init(cfg: M1Config, seed: int) -> np.ndarray:
+    w = np.empty(lib().orc_m1_weights_floats(C.byref(cfg)), np.float32)
+    lib().orc_m1_weights_init(C.byref(cfg), C.c_uint64(seed), _p(w))
+    return w
+
+
+def m1_layer_views(cfg: M1Config, w: np.ndarray):
+    """Named views of the flat weight buffer produced by m1_weights_init."""
+    dm, di, N, K, dr = cfg.d_model, cfg.d_inner, cfg.d_state, cfg.d_conv, cfg.dt_rank
+    xd = cfg.xdbl_dim
+    o = 0
+
+    def take(*shape):
+        nonlocal o
+        n = int(np.prod(shape))
+        v = w[o:o + n].reshape(shape)
+        o += n
+        return v
+
+    out = dict(input_proj_w=take(cfg.input_dim, dm), input_proj_b=take(dm), layers=[])
+    for _ in range(cfg.n_layers):
+        out["layers"].append(dict(
+            norm_w=take(dm), in_proj_w=take(dm, 2 * di), conv_w=take(di, K), conv_b=take(di),
+            x_proj_w=take(di, xd), dt_proj_w=take(dr, di), dt_proj_b=take(di),
+            a_log=take(di, N), a_neg=take(di, N), d_param=take(di), out_proj_w=take(di, dm)))
+    out["norm_f"] = take(dm)
+    assert o == w.size
+    return out
+
+
+def m1_prefill(cfg: M1Config, w, inp, conv_state=None, ssm_state=None, taps=False):
+    """One-sample backbone prefill.  inp [T,input_dim] -> out [T,d_model]."""
+    inp = _f32(inp)
+    T = inp.shape[0]
+    L, di, N, K = cfg.n_layers, cfg.d_inner, cfg.d_state, cfg.d_conv
+    cst = np.zeros((L, di, K), np.float32) if conv_state is None else _f32(conv_state).copy()
+    ssm = np.zeros((L, di, N), np.float32) if ssm_state is None else _f32(ssm_state).copy()
+    out = np.empty((T, cfg.d_model), np.float32)
+    tp = dict(proj=np.empty((L, T, 2 * di), np.float32),
+              delta_raw=np.empty((L, T, di), np.float32),
+              xdbl=np.empty((L, T, cfg.xdbl_dim), np.float32),
+              gated=np.empty((L, T, di), np.float32)) if taps else {}
+    lib().orc_m1_prefill(C.byref(cfg), _p(w), _p(inp), C.c_int(T), _p(cst), _p(ssm), _p(out),
+                         _p(tp.get("proj")), _p(tp.get("delta_raw")), _p(tp.get("xdbl")),
+                         _p(tp.get("gated")))
+    return dict(out=out, conv_state=cst, ssm_state=ssm, **tp)
+
+
+def m1_prefill_batch(cfg: M1Config, w, inp):
+    """Batch prefill, one OpenMP task per sample.  inp [B,T,input_dim]."""
+    inp = _f32(inp)
+    B, T = inp.shape[:2]
+    L, di = cfg.n_layers, cfg.d_inner
+    cst = np.zeros((B, L, di, cfg.d_conv), np.float32)
+    ssm = np.zeros((B, L, di, cfg.d_state), np.float32)
+    out = np.empty((B, T, cfg.d_model), np.float32)
+    nthr = lib().orc_m1_prefill_batch(C.byref(cfg), _p(w), _p(inp), C.c_int(B), C.c_int(T),
+                                      _p(cst), _p(ssm), _p(out))
+    return dict(out=out, conv_state=cst, ssm_state=ssm, threads=nthr)
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+# -- seeded test inputs ------------------------------------------------------
+
+def det_rand(n: int, seed: int) -> np.ndarray:
+    """xorshift32 stream in [-0.5, 0.5) used by the reference's kernel parity
+    tests (tests/m1_parallel_bwd_parity.rs:15-25)."""
+    s = np.uint32(seed)
+    out = np.empty(n, np.float32)
+    s = int(s)
+    for i in range(n):
+        s ^= (s << 13) & 0xFFFFFFFF
+        s ^= s >> 17
+        s ^= (s << 5) & 0xFFFFFFFF
+        out[i] = np.float32(s & 0xFFFF) / np.float32(65536.0) - np.float32(0.5)
+    return out
