@@ -26,6 +26,12 @@
 extern "C" {
 #endif
 
+#if defined(__GNUC__)
+#define MAMBA_B200_API __attribute__((visibility("default")))
+#else
+#define MAMBA_B200_API
+#endif
+
 #define MAMBA_B200_F32 0  /* WeightDtype::F32  */
 #define MAMBA_B200_F16 1  /* WeightDtype::F16  */
 #define MAMBA_B200_BF16 2 /* WeightDtype::Bf16 */
@@ -43,12 +49,12 @@ extern "C" {
  * init makes `device` current, raises the dynamic shared-memory limits of the
  * kernels and allocates one 4-byte device status word (the only allocation
  * the library ever makes). */
-int mamba_b200_init(int device, void** handle);
-int mamba_b200_destroy(void* handle);
-const char* mamba_b200_last_error(void* handle);
+MAMBA_B200_API int mamba_b200_init(int device, void** handle);
+MAMBA_B200_API int mamba_b200_destroy(void* handle);
+MAMBA_B200_API const char* mamba_b200_last_error(void* handle);
 /* Synchronously reads the device status word (bounded waits that gave up).
  * Returns 0 or MAMBA_B200_ERR_KERNEL.  Not graph-capturable; optional. */
-int mamba_b200_check_status(void* handle, void* stream);
+MAMBA_B200_API int mamba_b200_check_status(void* handle, void* stream);
 
 /*
  * Mamba-1 fused forward:
@@ -93,7 +99,7 @@ typedef struct mamba_b200_sscan_fwd_args {
     int save_stride;     /* multiple of 64 when chunk_states != NULL */
 } mamba_b200_sscan_fwd_args;
 
-int mamba_b200_sscan_fwd(void* handle, void* stream, const mamba_b200_sscan_fwd_args* args);
+MAMBA_B200_API int mamba_b200_sscan_fwd(void* handle, void* stream, const mamba_b200_sscan_fwd_args* args);
 
 /*
  * Reference-compatible unfused entry point: same argument list and meaning as
@@ -104,7 +110,7 @@ int mamba_b200_sscan_fwd(void* handle, void* stream, const mamba_b200_sscan_fwd_
  *   h[B,D,N] f32 in/out, y_out[B,T,D], delta (already softplus'ed), u, B, C
  *   [B,T,N] contiguous, a_neg[D,N], D[D].
  */
-int mamba_b200_ssm_scan_fwd_nosave(void* handle, void* stream, int dtype, float* h, void* y_out,
+MAMBA_B200_API int mamba_b200_ssm_scan_fwd_nosave(void* handle, void* stream, int dtype, float* h, void* y_out,
                                    const void* delta, const void* u, const void* B,
                                    const void* C, const float* a_neg, const float* D, int batch,
                                    int T, int d_inner, int d_state);

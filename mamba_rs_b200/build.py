@@ -50,7 +50,7 @@ def build(force: bool = False, verbose: bool = False, extra=()) -> str:
             sys.stderr.write(out.decode())
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
-    subprocess.check_call([nvcc, "--shared", "-o", LIB, *objs])
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "--shared", "-o", LIB, *objs])
     return LIB
 
 

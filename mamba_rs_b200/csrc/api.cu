@@ -45,7 +45,7 @@ int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limit
 
 using namespace mb200;
 
-extern "C" int mamba_b200_init(int device, void** handle) {
+extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     if (!handle) return MAMBA_B200_ERR_ARG;
     *handle = nullptr;
     Ctx* c = new (std::nothrow) Ctx();
@@ -73,7 +73,7 @@ extern "C" int mamba_b200_init(int device, void** handle) {
     return MAMBA_B200_OK;
 }
 
-extern "C" int mamba_b200_destroy(void* handle) {
+extern "C" MAMBA_B200_API int mamba_b200_destroy(void* handle) {
     Ctx* c = static_cast<Ctx*>(handle);
     if (!c) return MAMBA_B200_OK;
     if (c->d_status) {
@@ -84,12 +84,12 @@ extern "C" int mamba_b200_destroy(void* handle) {
     return MAMBA_B200_OK;
 }
 
-extern "C" const char* mamba_b200_last_error(void* handle) {
+extern "C" MAMBA_B200_API const char* mamba_b200_last_error(void* handle) {
     Ctx* c = static_cast<Ctx*>(handle);
     return c ? c->err : "null handle";
 }
 
-extern "C" int mamba_b200_check_status(void* handle, void* stream) {
+extern "C" MAMBA_B200_API int mamba_b200_check_status(void* handle, void* stream) {
     Ctx* c = static_cast<Ctx*>(handle);
     if (!c) return MAMBA_B200_ERR_ARG;
     int st = 0;

@@ -87,9 +87,17 @@ __device__ __forceinline__ float softplusf_fast(float v) {
 }
 
 // ---- packed f32x2 arithmetic (one issue slot for two lanes of FP32 work) ----
+#ifndef MB200_NO_F32X2
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+#else
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+#endif
 __device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
 
 // ---- mbarrier + TMA ----------------------------------------------------------

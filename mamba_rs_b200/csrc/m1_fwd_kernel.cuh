@@ -1,0 +1,507 @@
+// Mamba-1 fused selective-scan forward for sm_100a.
+//
+// One CTA owns (sample b, a tile of DT channels) and walks the sequence in
+// chunks of TC steps.  Per chunk:
+//   load   : TMA (cp.async.bulk.tensor.3d) brings the x / delta / z / B / C tiles
+//            of chunk c+1 into the other shared-memory stage while chunk c runs;
+//   stage 1: every thread, mapped over (t, channel pair): conv1d + SiLU,
+//            softplus(delta), SiLU(z), D skip -> f32 staging in shared memory;
+//   stage 2: thread = (group of CH channels, slice of NS states): the
+//            recurrence h = exp(delta*a)*h + delta*u*B, y = <h, C>, with h in
+//            registers and packed f32x2 arithmetic, reduced over the LPC lanes
+//            that share a channel; the lane with slice 0 applies gate and skip
+//            and writes the output tile;
+//   store  : TMA store of the y tile (clipped at T and D).
+// HBM is touched once per input and once per output element.
+#pragma once
+#include <string.h>
+
+#include <type_traits>
+#include <utility>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace mb200 {
+
+constexpr int kKMax = 8;  // widest supported d_conv
+
+struct FwdParams {
+    CUtensorMap tm_x, tm_dl, tm_z, tm_b, tm_c, tm_y;
+    const void *x, *dl, *z, *bm, *cm;
+    void *y, *u_out;
+    long long ld_x, ld_dl, ld_z, ld_bc, ld_y, ld_u;
+    const float *a_neg, *Dp, *conv_w, *conv_b;
+    float *conv_state, *ssm_state, *chunk_states;
+    int B, T, D, N, K;
+    int delta_softplus, z_mode, save_stride;
+    int u_vec;          // u_out rows allow paired stores
+    unsigned tma_mask;  // bit0 x, bit1 delta, bit2 z, bit3 B, bit4 C, bit5 y
+    int* status;
+};
+
+enum : unsigned { kTmaX = 1, kTmaDl = 2, kTmaZ = 4, kTmaB = 8, kTmaC = 16, kTmaY = 32 };
+
+template <typename Tact, int NS_, int LPC_, int WARPS_, int TC_>
+struct FwdTraits {
+    static constexpr int NS = NS_, LPC = LPC_, WARPS = WARPS_, TC = TC_;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int DT = THREADS / LPC;  // channels per CTA (one lane group per channel)
+    static constexpr int NP = NS * LPC;       // padded d_state
+    static constexpr int STAGES = 3;
+    static constexpr bool kConvertBC = sizeof(Tact) != 4;
+    static constexpr size_t al(size_t v) { return (v + 127) & ~size_t(127); }
+    static constexpr size_t RAW_ACT = al(sizeof(Tact) * TC * DT);
+    static constexpr size_t RAW_BC = al(sizeof(Tact) * TC * NP);
+    static constexpr size_t STAGE = 3 * RAW_ACT + 2 * RAW_BC;
+    static constexpr size_t OFF_RAW = 0;
+    static constexpr size_t OFF_BS = OFF_RAW + STAGES * STAGE;               // f32 B [TC][NP]
+    static constexpr size_t OFF_CS = OFF_BS + al(sizeof(float) * TC * NP);   // f32 C [TC][NP]
+    static constexpr size_t OFF_OUT = OFF_CS + al(sizeof(float) * TC * NP);  // 2 x Tact y [TC][DT]
+    static constexpr size_t OFF_BAR = OFF_OUT + 2 * RAW_ACT;                 // STAGES mbarriers
+    static constexpr size_t SMEM = OFF_BAR + 128;
+    static_assert(NS == 4 || NS == 8 || NS == 16, "state slice must be 4, 8 or 16");
+    static_assert((LPC & (LPC - 1)) == 0 && LPC <= 32, "LPC must be a power of two");
+    static_assert(TC % 4 == 0, "chunk must be a multiple of the 4-step block");
+};
+
+// Plain-load path for one tile (used when a tensor breaks a TMA layout rule).
+template <typename Tact>
+__device__ __forceinline__ void load_tile_plain(Tact* dst, const Tact* src, long long ld, int b,
+                                                int T, int t0, int c0, int cols, int rows,
+                                                int box_cols, int nthreads) {
+    const Tact zero = from_f<Tact>(0.0f);
+    for (int i = threadIdx.x; i < rows * box_cols; i += nthreads) {
+        int r = i / box_cols, c = i - r * box_cols;
+        int t = t0 + r, col = c0 + c;
+        Tact v = zero;
+        if (t < T && col < cols) v = src[(static_cast<long long>(b) * T + t) * ld + col];
+        dst[i] = v;
+    }
+}
+
+// FLAGS (compile-time, so that the hot block is one branch-free basic block):
+//   bit0 softplus on delta, bit1 gate present, bit2 conv1d + SiLU on x.
+template <typename Tr, typename Tact, int FLAGS>
+__global__ void __launch_bounds__(Tr::THREADS)
+sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
+    constexpr bool kSoftplus = (FLAGS & 1) != 0, kGate = (FLAGS & 2) != 0, kConv = (FLAGS & 4) != 0;
+    constexpr int NS = Tr::NS, LPC = Tr::LPC, TC = Tr::TC, DT = Tr::DT, NP = Tr::NP,
+                  THREADS = Tr::THREADS, STAGES = Tr::STAGES;
+    constexpr int RB = 4;  // timesteps whose elementwise work is done ahead of the recurrence
+    extern __shared__ __align__(128) unsigned char smem[];
+    float* Bs = reinterpret_cast<float*>(smem + Tr::OFF_BS);
+    float* Cs = reinterpret_cast<float*>(smem + Tr::OFF_CS);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Tr::OFF_BAR);
+
+    const int tid = threadIdx.x;
+    const int b = blockIdx.y;
+    const int d0 = blockIdx.x * DT;
+    const int T = p.T, D = p.D, N = p.N, K = kConv ? p.K : 0;
+    const int nchunks = (T + TC - 1) / TC;
+    const unsigned load_mask = p.tma_mask & (kTmaX | kTmaDl | kTmaZ | kTmaB | kTmaC);
+    constexpr bool has_z = kGate;
+    const bool gate_is_silu = p.z_mode == 1;
+
+    auto raw_x = [&](int s) { return reinterpret_cast<Tact*>(smem + Tr::OFF_RAW + s * Tr::STAGE); };
+    auto raw_dl = [&](int s) {
+        return reinterpret_cast<Tact*>(smem + Tr::OFF_RAW + s * Tr::STAGE + Tr::RAW_ACT);
+    };
+    auto raw_z = [&](int s) {
+        return reinterpret_cast<Tact*>(smem + Tr::OFF_RAW + s * Tr::STAGE + 2 * Tr::RAW_ACT);
+    };
+    auto raw_b = [&](int s) {
+        return reinterpret_cast<Tact*>(smem + Tr::OFF_RAW + s * Tr::STAGE + 3 * Tr::RAW_ACT);
+    };
+    auto raw_c = [&](int s) {
+        return reinterpret_cast<Tact*>(smem + Tr::OFF_RAW + s * Tr::STAGE + 3 * Tr::RAW_ACT +
+                                       Tr::RAW_BC);
+    };
+    auto out_tile = [&](int s) { return reinterpret_cast<Tact*>(smem + Tr::OFF_OUT + s * Tr::RAW_ACT); };
+
+    // Bytes one stage receives through TMA (full boxes: out-of-range parts are
+    // zero-filled and still counted).
+    uint32_t tx_bytes = 0;
+    if (load_mask & kTmaX) tx_bytes += sizeof(Tact) * TC * DT;
+    if (load_mask & kTmaDl) tx_bytes += sizeof(Tact) * TC * DT;
+    if (has_z && (load_mask & kTmaZ)) tx_bytes += sizeof(Tact) * TC * DT;
+    if (load_mask & kTmaB) tx_bytes += sizeof(Tact) * TC * N;
+    if (load_mask & kTmaC) tx_bytes += sizeof(Tact) * TC * N;
+
+    auto issue_loads = [&](int c) {  // one thread
+        const int s = c % STAGES, t0 = c * TC;
+        if (tx_bytes == 0) return;
+        mbar_expect_tx(&bars[s], tx_bytes);
+        if (load_mask & kTmaX) tma_load_3d(raw_x(s), &p.tm_x, &bars[s], d0, t0, b);
+        if (load_mask & kTmaDl) tma_load_3d(raw_dl(s), &p.tm_dl, &bars[s], d0, t0, b);
+        if (has_z && (load_mask & kTmaZ)) tma_load_3d(raw_z(s), &p.tm_z, &bars[s], d0, t0, b);
+        if (load_mask & kTmaB) tma_load_3d(raw_b(s), &p.tm_b, &bars[s], 0, t0, b);
+        if (load_mask & kTmaC) tma_load_3d(raw_c(s), &p.tm_c, &bars[s], 0, t0, b);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (nchunks > 0) issue_loads(0);
+        if (nchunks > 1) issue_loads(1);
+    }
+
+    // ---- ownership: LPC lanes per channel, NS states per lane ----
+    // Up to 16 states live in one lane (LPC = 1: no shuffles, no divergence);
+    // larger d_state spreads a channel over LPC lanes that all repeat the cheap
+    // per-(t, channel) elementwise work and reduce y with shuffles.
+    const int col = tid / LPC, part = tid % LPC;
+    const int d = d0 + col;
+    const bool d_ok = d < D;
+    const int n0 = part * NS;
+    float2 h[NS / 2];
+    float2 a2[NS / 2];  // a_neg * log2(e)
+    bool geo_local = true;
+    {
+        float av[NS], hv[NS];
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+            const int n = n0 + j;
+            const bool ok = d_ok && n < N;
+            av[j] = ok ? p.a_neg[static_cast<long long>(d) * N + n] * kLog2e : 0.0f;
+            hv[j] = (ok && p.ssm_state) ? p.ssm_state[(static_cast<long long>(b) * D + d) * N + n]
+                                        : 0.0f;
+        }
+        // Arithmetic-progression test a[n] = a[n0] + (n-n0)*step, to 4 ulp: then
+        // exp(delta*a[n]) = E * R^(n-n0) and a step needs 2-3 exp2 instead of NS.
+        const float step = av[1] - av[0];
+#pragma unroll
+        for (int j = 2; j < NS; ++j) {
+            const float pred = fmaf(static_cast<float>(j), step, av[0]);
+            if (fabsf(av[j] - pred) > 4.8e-7f * fabsf(av[j])) geo_local = false;
+        }
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            a2[j] = make_float2(av[2 * j], av[2 * j + 1]);
+            h[j] = make_float2(hv[2 * j], hv[2 * j + 1]);
+        }
+    }
+    const bool geo = __all_sync(0xffffffffu, geo_local ? 1 : 0) != 0;  // per warp
+    const float a2_first = a2[0].x, a2_step = a2[0].y - a2[0].x;
+    const float a2_mid = a2[NS / 4].x;  // second seed of the power chain (NS == 16)
+    (void)a2_mid;
+    const float Dd = d_ok ? p.Dp[d] : 0.0f;
+    // conv taps and the sliding window (oldest -> newest), right-aligned:
+    // tap k of K sits at index kKMax-K+k.
+    float cw[kKMax], win[kKMax];
+    float cb = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kKMax; ++k) {
+        const int kk = k - (kKMax - K);
+        cw[k] = (kk >= 0 && d_ok) ? p.conv_w[static_cast<long long>(d) * K + kk] : 0.0f;
+        win[k] = (kk >= 0 && d_ok && p.conv_state)
+                     ? p.conv_state[(static_cast<long long>(b) * D + d) * K + kk]
+                     : 0.0f;
+    }
+    if (K && d_ok) cb = p.conv_b[d];
+
+    const long long save_chunks = p.chunk_states ? (T + p.save_stride - 1) / p.save_stride : 0;
+
+    // Per-timestep values produced by the elementwise stage.
+    struct Elem {
+        float dl, du, g, sk;
+    };
+
+    for (int c = 0; c < nchunks; ++c) {
+        const int s = c % STAGES, t0 = c * TC;
+        const int nv = min(TC, T - t0);
+        if (tid == 0 && c + 2 < nchunks) issue_loads(c + 2);
+        // Tensors that could not be described to TMA: cooperative plain loads.
+        const bool any_plain = load_mask != (kTmaX | kTmaDl | kTmaZ | kTmaB | kTmaC);
+        if (any_plain) {
+            if (!(load_mask & kTmaX))
+                load_tile_plain(raw_x(s), static_cast<const Tact*>(p.x), p.ld_x, b, T, t0, d0, D, TC,
+                                DT, THREADS);
+            if (!(load_mask & kTmaDl))
+                load_tile_plain(raw_dl(s), static_cast<const Tact*>(p.dl), p.ld_dl, b, T, t0, d0, D,
+                                TC, DT, THREADS);
+            if (has_z && !(load_mask & kTmaZ))
+                load_tile_plain(raw_z(s), static_cast<const Tact*>(p.z), p.ld_z, b, T, t0, d0, D, TC,
+                                DT, THREADS);
+            if (!(load_mask & kTmaB))
+                load_tile_plain(raw_b(s), static_cast<const Tact*>(p.bm), p.ld_bc, b, T, t0, 0, N,
+                                TC, N, THREADS);
+            if (!(load_mask & kTmaC))
+                load_tile_plain(raw_c(s), static_cast<const Tact*>(p.cm), p.ld_bc, b, T, t0, 0, N,
+                                TC, N, THREADS);
+            __syncthreads();
+        }
+        if (tx_bytes) mbar_wait(&bars[s], (c / STAGES) & 1, p.status);
+
+        // B / C of the chunk -> f32, zero-padded to NP columns (shared by the CTA).
+        {
+            const Tact* rb = raw_b(s);
+            const Tact* rc = raw_c(s);
+            for (int i = tid; i < TC * NP; i += THREADS) {
+                const int r = i / NP, n = i - r * NP;
+                Bs[i] = n < N ? to_f(rb[r * N + n]) : 0.0f;
+                Cs[i] = n < N ? to_f(rc[r * N + n]) : 0.0f;
+            }
+        }
+        __syncthreads();
+
+        // Training save: state entering each block of save_stride steps.
+        if (p.chunk_states && (t0 % p.save_stride) == 0) {
+            const long long sc = t0 / p.save_stride;
+#pragma unroll
+            for (int j = 0; j < NS; ++j) {
+                const int n = n0 + j;
+                if (d_ok && n < N)
+                    p.chunk_states[((static_cast<long long>(b) * save_chunks + sc) * D + d) * N + n] =
+                        (j & 1) ? h[j / 2].y : h[j / 2].x;
+            }
+        }
+
+        const Tact* rx = raw_x(s) + col;
+        const Tact* rd = raw_dl(s) + col;
+        const Tact* rz = raw_z(s) + col;
+        Tact* ot = out_tile(c & 1) + col;
+        const float* Bp = Bs + n0;
+        const float* Cp = Cs + n0;
+
+        // Elementwise stage of one timestep (row r of the chunk).
+        auto elem = [&](int r) -> Elem {
+            float u = to_f(rx[r * DT]);
+            if (kConv) {
+#pragma unroll
+                for (int k = 0; k < kKMax - 1; ++k) win[k] = win[k + 1];
+                win[kKMax - 1] = u;
+                float acc = cb;
+#pragma unroll
+                for (int k = 0; k < kKMax; ++k) acc = fmaf(win[k], cw[k], acc);
+                u = siluf_fast(acc);
+                if (p.u_out && d_ok && part == 0)
+                    static_cast<Tact*>(p.u_out)[(static_cast<long long>(b) * T + t0 + r) * p.ld_u + d] =
+                        from_f<Tact>(u);
+            }
+            float dv = to_f(rd[r * DT]);
+            if (kSoftplus) dv = softplusf_fast(dv);
+            float gv = 1.0f;
+            if (kGate) {
+                const float zv = to_f(rz[r * DT]);
+                const float sz = siluf_fast(zv);
+                gv = gate_is_silu ? sz : zv;  // select, not a branch
+            }
+            Elem o;
+            o.dl = dv;
+            o.du = dv * u;
+            o.g = gv;
+            o.sk = Dd * u * gv;
+            return o;
+        };
+
+        // Recurrence of NB timesteps starting at row r0; B/C of the whole block are
+        // fetched first so that their latency overlaps the arithmetic.
+        auto recur = [&](auto geo_tag, auto nb_tag, int r0, const Elem* el) {
+            constexpr bool GEO = decltype(geo_tag)::value;
+            constexpr int NB = decltype(nb_tag)::value;
+            float4 Bq[NB][NS / 4], Cq[NB][NS / 4];
+#pragma unroll
+            for (int i = 0; i < NB; ++i)
+#pragma unroll
+                for (int j = 0; j < NS / 4; ++j) {
+                    Bq[i][j] = *reinterpret_cast<const float4*>(Bp + (r0 + i) * NP + 4 * j);
+                    Cq[i][j] = *reinterpret_cast<const float4*>(Cp + (r0 + i) * NP + 4 * j);
+                }
+            float yo[NB];
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                float2 e[NS / 2];
+                if (GEO) {
+                    // e[j] = (E R^(2j), E R^(2j+1)): product tree of depth <= 3,
+                    // re-seeded at the middle state when NS == 16.
+                    const float R = ex2(el[i].dl * a2_step);
+                    const float R2 = R * R;
+                    const float2 r2 = splat2(R2), r4 = splat2(R2 * R2);
+                    const float E0 = ex2(el[i].dl * a2_first);
+                    e[0] = make_float2(E0, E0 * R);
+                    e[1] = mul2(e[0], r2);
+                    if (NS >= 8) {
+                        e[2] = mul2(e[0], r4);
+                        e[3] = mul2(e[1], r4);
+                    }
+                    if (NS == 16) {
+                        const float E1 = ex2(el[i].dl * a2_mid);
+                        e[4] = make_float2(E1, E1 * R);
+                        e[5] = mul2(e[4], r2);
+                        e[6] = mul2(e[4], r4);
+                        e[7] = mul2(e[5], r4);
+                    }
+                } else {
+                    const float2 dl2 = splat2(el[i].dl);
+#pragma unroll
+                    for (int j = 0; j < NS / 2; ++j) {
+                        const float2 xa = mul2(dl2, a2[j]);
+                        e[j] = make_float2(ex2(xa.x), ex2(xa.y));
+                    }
+                }
+                const float2 du2 = splat2(el[i].du);
+                float2 dub[NS / 2];
+#pragma unroll
+                for (int j = 0; j < NS / 4; ++j) {
+                    dub[2 * j] = mul2(du2, make_float2(Bq[i][j].x, Bq[i][j].y));
+                    dub[2 * j + 1] = mul2(du2, make_float2(Bq[i][j].z, Bq[i][j].w));
+                }
+#pragma unroll
+                for (int j = 0; j < NS / 2; ++j) h[j] = fma2(e[j], h[j], dub[j]);
+                float2 yp[NS / 2];
+#pragma unroll
+                for (int j = 0; j < NS / 4; ++j) {
+                    yp[2 * j] = mul2(h[2 * j], make_float2(Cq[i][j].x, Cq[i][j].y));
+                    yp[2 * j + 1] = mul2(h[2 * j + 1], make_float2(Cq[i][j].z, Cq[i][j].w));
+                }
+#pragma unroll
+                for (int w = NS / 4; w >= 1; w >>= 1)
+#pragma unroll
+                    for (int j = 0; j < w; ++j) yp[j] = add2(yp[j], yp[j + w]);
+                float y = yp[0].x + yp[0].y;
+#pragma unroll
+                for (int m = 1; m < LPC; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
+                yo[i] = fmaf(y, el[i].g, el[i].sk);
+            }
+            // Stores after every load of the block.
+            if (part == 0) {
+#pragma unroll
+                for (int i = 0; i < NB; ++i) ot[(r0 + i) * DT] = from_f<Tact>(yo[i]);
+            }
+        };
+        auto run = [&](auto geo_tag) {
+            if (nv == TC) {
+                Elem cur[RB], nxt[RB];
+#pragma unroll
+                for (int i = 0; i < RB; ++i) cur[i] = elem(i);
+                // Every iteration but the last also does the elementwise work of the
+                // following block; it is independent of this block's recurrence and
+                // sits in the same basic block, so the two interleave.
+#pragma unroll 1
+                for (int r0 = 0; r0 < TC - RB; r0 += RB) {
+#pragma unroll
+                    for (int i = 0; i < RB; ++i) nxt[i] = elem(r0 + RB + i);
+                    recur(geo_tag, std::integral_constant<int, RB>{}, r0, cur);
+#pragma unroll
+                    for (int i = 0; i < RB; ++i) cur[i] = nxt[i];
+                }
+                recur(geo_tag, std::integral_constant<int, RB>{}, TC - RB, cur);
+            } else {
+#pragma unroll 1
+                for (int r0 = 0; r0 < nv; ++r0) {
+                    Elem one = elem(r0);
+                    recur(geo_tag, std::integral_constant<int, 1>{}, r0, &one);
+                }
+            }
+        };
+        if (geo) run(std::true_type{});
+        else run(std::false_type{});
+
+        // ---------------- store the y tile ----------------
+        if (p.tma_mask & kTmaY) {
+            fence_proxy_async();
+            __syncthreads();
+            if (tid == 0) {
+                tma_store_3d(&p.tm_y, out_tile(c & 1), d0, t0, b);
+                tma_commit();
+                // the other y buffer (written next) must have been fully read
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
+        } else {
+            __syncthreads();
+            Tact* yb = static_cast<Tact*>(p.y);
+            const Tact* o = out_tile(c & 1);
+            for (int i = tid; i < nv * DT; i += THREADS) {
+                const int r = i / DT, cidx = i - r * DT;
+                if (d0 + cidx < D)
+                    yb[(static_cast<long long>(b) * T + t0 + r) * p.ld_y + d0 + cidx] = o[i];
+            }
+        }
+    }
+
+    // Final recurrent state and conv window.
+    if (p.ssm_state) {
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+            const int n = n0 + j;
+            if (d_ok && n < N)
+                p.ssm_state[(static_cast<long long>(b) * D + d) * N + n] =
+                    (j & 1) ? h[j / 2].y : h[j / 2].x;
+        }
+    }
+    if (K && p.conv_state && d_ok && part == 0) {
+        for (int k = 0; k < K; ++k)
+            p.conv_state[(static_cast<long long>(b) * D + d) * K + k] = win[kKMax - K + k];
+    }
+    if (tid == 0) tma_wait_read0();  // shared memory must outlive the last bulk store
+}
+
+typedef void (*FwdKernelFn)(const FwdParams);
+
+struct FwdVariant {
+    int ns, lpc, dt, tc, threads;
+    size_t smem;          // dynamic shared memory of this dtype's layout
+    FwdKernelFn fn[8];    // by FLAGS
+};
+
+#ifndef MB200_FWD_WARPS
+#define MB200_FWD_WARPS 2
+#endif
+#ifndef MB200_FWD_TC
+#define MB200_FWD_TC 16
+#endif
+
+template <typename Tr, typename Tact, int... F>
+static void fill_flags(FwdKernelFn* out, std::integer_sequence<int, F...>) {
+    ((out[F] = sscan_fwd_kernel<Tr, Tact, F>), ...);
+}
+
+template <typename Tact, int NS, int LPC>
+static FwdVariant make_variant() {
+    using Tr = FwdTraits<Tact, NS, LPC, MB200_FWD_WARPS, MB200_FWD_TC>;
+    FwdVariant v;
+    memset(&v, 0, sizeof(v));
+    v.ns = NS; v.lpc = LPC; v.dt = Tr::DT; v.tc = Tr::TC; v.threads = Tr::THREADS;
+    v.smem = Tr::SMEM;
+#ifdef MB200_FWD_TUNING  // tuning builds: compat (0) and fused-no-conv (3) only
+    fill_flags<Tr, Tact>(v.fn, std::integer_sequence<int, 0, 3>{});
+#else
+    fill_flags<Tr, Tact>(v.fn, std::make_integer_sequence<int, 8>{});
+#endif
+    return v;
+}
+
+// Variants of one storage dtype, ordered by padded d_state: up to 16 states per
+// lane; above that LPC lanes share a channel.
+template <typename Tact>
+static int build_fwd_variants(FwdVariant* v) {
+    int n = 0;
+#ifndef MB200_FWD_TUNING
+    v[n++] = make_variant<Tact, 4, 1>();
+    v[n++] = make_variant<Tact, 8, 1>();
+#endif
+#ifdef MB200_FWD_NS8X2
+    v[n++] = make_variant<Tact, 8, 2>();
+#else
+    v[n++] = make_variant<Tact, 16, 1>();
+#endif
+#ifndef MB200_FWD_TUNING
+    v[n++] = make_variant<Tact, 16, 2>();
+    v[n++] = make_variant<Tact, 16, 4>();
+    v[n++] = make_variant<Tact, 16, 8>();
+    v[n++] = make_variant<Tact, 16, 16>();
+#endif
+    return n;
+}
+
+constexpr int kMaxFwdVariants = 8;
+// One translation unit per storage dtype defines its table (parallel builds).
+int fwd_variants_f32(FwdVariant* v);
+int fwd_variants_f16(FwdVariant* v);
+int fwd_variants_bf16(FwdVariant* v);
+
+}  // namespace mb200

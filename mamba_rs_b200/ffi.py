@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB = os.path.join(HERE, "libmamba_b200.so")
+# MAMBA_B200_LIB selects another build of the same ABI (tuning builds).
+_LIB = os.environ.get("MAMBA_B200_LIB") or os.path.join(HERE, "libmamba_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 
