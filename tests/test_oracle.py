@@ -1,0 +1,233 @@
+"""CPU tests of the oracle itself: it must satisfy the properties the
+reference's own tests pin (it has no stored golden vectors for this path) and
+reproduce the committed fixtures."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import GOLDEN_CASES, golden_inputs, load_golden, quantised_inputs, random_states, rel_err
+
+
+# --- src/ops/fast_math.rs:263-341 (the reference's own unit tests) -----------
+
+def test_fast_exp_scalar_accuracy():
+    xs = (np.arange(-800, 201) * 0.1).astype(np.float32)
+    fast = oracle.fast_exp(xs).astype(np.float64)
+    exact = np.exp(xs.astype(np.float64))
+    m = exact > 1e-30
+    assert np.max(np.abs(fast[m] - exact[m]) / exact[m]) < 2e-7
+
+
+def test_fast_exp_inplace_accuracy():
+    buf = (np.arange(-400, 101) * 0.1).astype(np.float32)
+    fast = oracle.fast_exp_inplace(buf).astype(np.float64)
+    exact = np.exp(buf).astype(np.float64)
+    m = exact > 1e-30
+    assert np.max(np.abs(fast[m] - exact[m]) / exact[m]) < 2e-7
+
+
+def test_fast_exp_edge_cases():
+    fe = lambda v: float(oracle.fast_exp(np.float32(v))[0])
+    # libm expf is correctly rounded here; numpy's vectorised float32 exp is not
+    ex = lambda v: float(np.float32(np.exp(np.float64(np.float32(v)))))
+    assert fe(-100.0) >= 0.0 and np.isfinite(fe(-100.0)) and np.isfinite(fe(100.0))
+    assert abs(fe(0.0) - 1.0) < 1e-8
+    assert abs(fe(-0.01) - ex(-0.01)) < 1e-8
+    assert abs(fe(-0.5) - ex(-0.5)) < 1e-7
+    assert abs(fe(-1.0) - ex(-1.0)) < 1e-7
+
+
+def test_fast_exp_ssm_range():
+    xs = (-np.arange(1000) * 0.08).astype(np.float32)
+    fast = oracle.fast_exp(xs).astype(np.float64)
+    exact = np.exp(xs).astype(np.float64)
+    m = exact > 1e-30
+    assert np.max(np.abs(fast[m] - exact[m]) / exact[m]) < 2e-7
+
+
+def test_fast_exp_simd_lane_matches_scalar_to_1ulp():
+    xs = np.linspace(-30, 5, 4001).astype(np.float32)
+    a = oracle.fast_exp(xs)
+    b = oracle.fast_exp(xs, simd=True)
+    assert np.max(np.abs(a.astype(np.float64) - b) / a) < 2.5e-7
+
+
+# --- seeded weights, src/weights.rs:107-160, :224-250 --------------------------
+
+def test_weights_init_follows_reference_rng():
+    cfg = oracle.m1_config(d_model=128, n_layers=2, d_state=16, d_conv=4, expand=2, input_dim=128)
+    assert cfg.dt_rank == 8 and cfg.d_inner == 256 and cfg.xdbl_dim == 40
+    w = oracle.m1_weights_init(cfg, 42)
+    v = oracle.m1_layer_views(cfg, w)
+    # independent restatement of the LCG for the first input_proj entries
+    st, vals = 42, []
+    for _ in range(4):
+        st = (st * 6364136223846793005 + 1442695040888963407) % (1 << 64)
+        vals.append(np.float32(st >> 40) / np.float32(1 << 24))
+    bound = np.sqrt(np.float32(3.0) / np.float32(128))
+    np.testing.assert_array_equal(v["input_proj_w"].ravel()[:4],
+                                  np.float32(-bound) + np.float32(2) * bound * np.array(vals, np.float32))
+    for lw in v["layers"]:
+        np.testing.assert_allclose(lw["a_log"], np.tile(np.log(np.arange(1, 17, dtype=np.float32)), (256, 1)))
+        np.testing.assert_allclose(lw["a_neg"], -np.tile(np.arange(1, 17, dtype=np.float32), (256, 1)), rtol=3e-7)
+        assert np.all(lw["d_param"] == 1.0) and np.all(lw["norm_w"] == 1.0) and np.all(lw["conv_b"] == 0.0)
+        dt = np.log1p(np.exp(lw["dt_proj_b"].astype(np.float64)))  # softplus(bias) = sampled dt
+        assert dt.min() >= 1e-3 * 0.999 and dt.max() <= 1e-1 * 1.001
+        assert np.abs(lw["in_proj_w"]).max() <= np.sqrt(3.0 / 128) + 1e-6
+    assert np.all(v["norm_f"] == 1.0) and np.all(v["input_proj_b"] == 0.0)
+
+
+# --- f32 oracle vs f64 shadow ---------------------------------------------------
+
+@pytest.mark.parametrize("K", [0, 4])
+def test_forward_matches_f64_shadow(K):
+    q = quantised_inputs(2, 64, 24, 16, K, "f32", seed=3, a_mode="random")
+    ssm0, cst0 = random_states(2, 24, 16, K, 4)
+    args = (q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"],
+            q.get("conv_w"), q.get("conv_b"), cst0, ssm0)
+    r32 = oracle.m1_fused_fwd(*args)
+    r64 = oracle.m1_fused_fwd_f64(*args)
+    assert rel_err(r32["y"], r64["y"]) < 2e-6
+    assert rel_err(r32["ssm_state"], r64["ssm_state"]) < 2e-6
+
+
+# --- tests/prefill.rs:90-168, :174-232: split == whole, step loop == sequence ----
+
+def test_split_sequence_equals_whole_bitwise():
+    q = quantised_inputs(2, 48, 16, 16, 4, "f32", seed=5)
+    a = (q["a_neg"], q["Dp"], q["conv_w"], q["conv_b"])
+    whole = oracle.m1_fused_fwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], *a)
+    h1 = oracle.m1_fused_fwd(q["x"][:, :20], q["delta_raw"][:, :20], q["Bm"][:, :20], q["Cm"][:, :20],
+                             q["z"][:, :20], *a)
+    h2 = oracle.m1_fused_fwd(q["x"][:, 20:], q["delta_raw"][:, 20:], q["Bm"][:, 20:], q["Cm"][:, 20:],
+                             q["z"][:, 20:], *a, conv_state=h1["conv_state"], ssm_state=h1["ssm_state"])
+    np.testing.assert_array_equal(np.concatenate([h1["y"], h2["y"]], axis=1), whole["y"])
+    np.testing.assert_array_equal(h2["ssm_state"], whole["ssm_state"])
+    np.testing.assert_array_equal(h2["conv_state"], whole["conv_state"])
+
+
+def test_step_loop_tracks_sequence_forward():
+    # The reference pins this hand-off by cosine > 0.9999 / max-rel < 1e-2 (the
+    # step path sums the conv taps in another order); we hold it to 1e-5.
+    q = quantised_inputs(2, 24, 12, 16, 4, "f32", seed=6)
+    a = (q["a_neg"], q["Dp"], q["conv_w"], q["conv_b"])
+    seq = oracle.m1_fused_fwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], *a)
+    ssm = np.zeros((2, 12, 16), np.float32)
+    cst = np.zeros((2, 12, 4), np.float32)
+    ys = []
+    for t in range(24):
+        r = oracle.m1_step(q["x"][:, t], q["delta_raw"][:, t], q["Bm"][:, t], q["Cm"][:, t], q["z"][:, t],
+                           *a, conv_state=cst, ssm_state=ssm)
+        ssm, cst = r["ssm_state"], r["conv_state"]
+        ys.append(r["y"])
+    assert rel_err(np.stack(ys, axis=1), seq["y"]) < 1e-5
+    assert rel_err(ssm, seq["ssm_state"]) < 1e-5
+    np.testing.assert_array_equal(cst, seq["conv_state"])
+
+
+# --- tests/grad_oracle.rs: analytic backward vs f64 central differences -----------
+
+def test_backward_matches_f64_finite_differences():
+    rng = np.random.default_rng(0)
+    B, T, D, N, K = 2, 30, 8, 16, 4
+    q = quantised_inputs(B, T, D, N, K, "f32", seed=7, a_mode="random")
+    dg = rng.standard_normal((B, T, D)).astype(np.float32)
+    names = dict(x="x", delta="delta_raw", Bm="Bm", Cm="Cm", z="z", a_neg="a_neg", Dp="Dp",
+                 conv_w="conv_w", conv_b="conv_b")
+    base = {k: q[v].astype(np.float64) for k, v in names.items()}
+    g = oracle.m1_fused_bwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"], dg,
+                            q["conv_w"], q["conv_b"])
+
+    def loss(**kw):
+        a = dict(base)
+        a.update(kw)
+        return float((oracle.m1_fused_fwd_f64(**a)["y"] * dg).sum())
+
+    checks = [("x", "d_x"), ("delta", "d_delta"), ("z", "d_z"), ("Bm", "dB"), ("Cm", "dC"),
+              ("Dp", "dD"), ("conv_w", "dconv_w"), ("conv_b", "dconv_b")]
+    eps = 1e-4
+    for name, gname in checks:
+        for _ in range(4):
+            idx = tuple(int(rng.integers(0, s)) for s in base[name].shape)
+            ap, am = base[name].copy(), base[name].copy()
+            ap[idx] += eps
+            am[idx] -= eps
+            fd = (loss(**{name: ap}) - loss(**{name: am})) / (2 * eps)
+            an = float(g[gname][idx])
+            assert abs(fd - an) <= 5e-3 * max(abs(fd), abs(an)) + 2e-5, (name, idx, fd, an)
+    a_log = np.log(-base["a_neg"])
+    for _ in range(4):
+        idx = tuple(int(rng.integers(0, s)) for s in a_log.shape)
+        ap, am = a_log.copy(), a_log.copy()
+        ap[idx] += eps
+        am[idx] -= eps
+        fd = (loss(a_neg=-np.exp(ap)) - loss(a_neg=-np.exp(am))) / (2 * eps)
+        an = float(g["dA_log"][idx])
+        assert abs(fd - an) <= 5e-3 * max(abs(fd), abs(an)) + 2e-5, ("a_log", idx, fd, an)
+
+
+# --- BASELINE config #1: backbone prefill, batch == per-sample, taps feed the fused op ---
+
+def test_backbone_prefill_config1_consistency():
+    cfg = oracle.m1_config(d_model=128, n_layers=2, d_state=16, d_conv=4, expand=2, input_dim=128)
+    w = oracle.m1_weights_init(cfg, 42)
+    inp = np.random.default_rng(7).standard_normal((2, 96, 128)).astype(np.float32)
+    one = [oracle.m1_prefill(cfg, w, inp[b], taps=True) for b in range(2)]
+    batch = oracle.m1_prefill_batch(cfg, w, inp)
+    for b in range(2):
+        np.testing.assert_array_equal(batch["out"][b], one[b]["out"])
+        np.testing.assert_array_equal(batch["ssm_state"][b], one[b]["ssm_state"])
+    assert np.isfinite(batch["out"]).all()
+    # each position of the output is RMS-normalised with unit weights
+    np.testing.assert_allclose(np.sqrt((batch["out"] ** 2).mean(-1)), 1.0, rtol=1e-3)
+    # the per-layer taps reproduce the layer's gated output through the fused op alone
+    v = oracle.m1_layer_views(cfg, w)
+    di, N, dr = cfg.d_inner, cfg.d_state, cfg.dt_rank
+    t = one[0]
+    for l, lw in enumerate(v["layers"]):
+        proj, xdbl = t["proj"][l], t["xdbl"][l]
+        r = oracle.m1_fused_fwd(proj[None, :, :di], t["delta_raw"][l][None], xdbl[None, :, dr:dr + N],
+                                xdbl[None, :, dr + N:], proj[None, :, di:], lw["a_neg"], lw["d_param"],
+                                lw["conv_w"], lw["conv_b"])
+        np.testing.assert_array_equal(r["y"][0], t["gated"][l])
+        np.testing.assert_array_equal(r["ssm_state"][0], t["ssm_state"][l])
+
+
+def test_prefill_then_continue_equals_whole():
+    cfg = oracle.m1_config(d_model=64, n_layers=2, d_state=8, d_conv=4, expand=2, input_dim=64)
+    w = oracle.m1_weights_init(cfg, 1)
+    inp = np.random.default_rng(8).standard_normal((40, 64)).astype(np.float32)
+    whole = oracle.m1_prefill(cfg, w, inp)
+    a = oracle.m1_prefill(cfg, w, inp[:17])
+    b = oracle.m1_prefill(cfg, w, inp[17:], conv_state=a["conv_state"], ssm_state=a["ssm_state"])
+    np.testing.assert_array_equal(np.concatenate([a["out"], b["out"]]), whole["out"])
+    np.testing.assert_array_equal(b["ssm_state"], whole["ssm_state"])
+
+
+# --- committed fixtures ------------------------------------------------------------
+
+@pytest.mark.parametrize("case", GOLDEN_CASES, ids=[c[0] for c in GOLDEN_CASES])
+def test_oracle_reproduces_golden(case):
+    q, ssm0, cst0, dg = golden_inputs(case)
+    gold = load_golden(case[0])
+    fwd = oracle.m1_fused_fwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"],
+                              q.get("conv_w"), q.get("conv_b"), cst0, ssm0)
+    np.testing.assert_array_equal(fwd["y"], gold["y"])
+    np.testing.assert_array_equal(fwd["ssm_state"], gold["ssm_state"])
+    bwd = oracle.m1_fused_bwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"], dg,
+                              q.get("conv_w"), q.get("conv_b"), cst0, ssm0)
+    for k in ("d_x", "d_delta", "d_z", "dB", "dC", "dA_log", "dD"):
+        np.testing.assert_array_equal(bwd[k], gold[k])
+
+
+def test_det_rand_stream():
+    # tests/m1_parallel_bwd_parity.rs:15-25: xorshift32, (s & 0xFFFF) / 65536 - 0.5
+    v = oracle.det_rand(4, 1)
+    s, exp = 1, []
+    for _ in range(4):
+        s ^= (s << 13) & 0xFFFFFFFF
+        s ^= s >> 17
+        s ^= (s << 5) & 0xFFFFFFFF
+        exp.append((s & 0xFFFF) / 65536.0 - 0.5)
+    np.testing.assert_allclose(v, exp, rtol=0, atol=1e-7)
+    assert np.all(v >= -0.5) and np.all(v < 0.5)
