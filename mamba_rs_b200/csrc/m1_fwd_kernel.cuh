@@ -55,14 +55,69 @@ struct FwdTraits {
     static constexpr size_t RAW_BC = al(sizeof(Tact) * TC * NP);
     static constexpr size_t STAGE = 3 * RAW_ACT + 2 * RAW_BC;
     static constexpr size_t OFF_RAW = 0;
-    static constexpr size_t OFF_BS = OFF_RAW + STAGES * STAGE;               // f32 B [TC][NP]
-    static constexpr size_t OFF_CS = OFF_BS + al(sizeof(float) * TC * NP);   // f32 C [TC][NP]
-    static constexpr size_t OFF_OUT = OFF_CS + al(sizeof(float) * TC * NP);  // 2 x Tact y [TC][DT]
-    static constexpr size_t OFF_BAR = OFF_OUT + 2 * RAW_ACT;                 // STAGES mbarriers
+    static constexpr size_t OFF_BS = OFF_RAW + STAGES * STAGE;  // B [TC][NP] zero-padded (N != NP only)
+    static constexpr size_t OFF_CS = OFF_BS + RAW_BC;           // C [TC][NP] zero-padded
+    static constexpr size_t OFF_OUT = OFF_CS + RAW_BC;          // 2 x Tact y [TC][DT]
+    static constexpr size_t OFF_HALO = OFF_OUT + 2 * RAW_ACT;                // f32 conv window [kKMax][DT]
+    static constexpr size_t OFF_BAR = OFF_HALO + al(sizeof(float) * kKMax * DT);  // STAGES mbarriers
     static constexpr size_t SMEM = OFF_BAR + 128;
+    // Timesteps per block of the hot loop, and how the per-(t, channel)
+    // elementwise work is spread: with 2 or 4 lanes per channel each lane does
+    // it for the rows r = part (mod LPC) of a block and the results are
+    // exchanged with shuffles; otherwise every lane repeats it.
+    static constexpr int RB = 4;
+    static constexpr bool SHARE = (LPC == 2 || LPC == 4);
+    static constexpr int OWN = SHARE ? RB / LPC : RB;
     static_assert(NS == 4 || NS == 8 || NS == 16, "state slice must be 4, 8 or 16");
     static_assert((LPC & (LPC - 1)) == 0 && LPC <= 32, "LPC must be a power of two");
     static_assert(TC % 4 == 0, "chunk must be a multiple of the 4-step block");
+};
+
+// NS consecutive B or C values of one timestep, held in registers in their
+// storage dtype and widened to f32 pairs at the point of use.
+template <typename Tact, int NS>
+struct StateVec;
+template <int NS>
+struct StateVec<float, NS> {
+    float4 q[NS / 4];
+    __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+        for (int j = 0; j < NS / 4; ++j) q[j] = *reinterpret_cast<const float4*>(p + 4 * j);
+    }
+    __device__ __forceinline__ float2 pair(int j) const {
+        return (j & 1) ? make_float2(q[j / 2].z, q[j / 2].w) : make_float2(q[j / 2].x, q[j / 2].y);
+    }
+};
+template <typename Th, int NS>
+struct StateVecHalf {
+    uint32_t w[NS / 2];  // two 16-bit elements per word
+    __device__ __forceinline__ void load(const Th* p) {
+        if (NS % 8 == 0) {
+#pragma unroll
+            for (int j = 0; j < NS / 8; ++j) {
+                const uint4 v = *reinterpret_cast<const uint4*>(p + 8 * j);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NS / 4; ++j) {
+                const uint2 v = *reinterpret_cast<const uint2*>(p + 4 * j);
+                w[2 * j] = v.x; w[2 * j + 1] = v.y;
+            }
+        }
+    }
+};
+template <int NS>
+struct StateVec<__nv_bfloat16, NS> : StateVecHalf<__nv_bfloat16, NS> {
+    __device__ __forceinline__ float2 pair(int j) const {
+        return make_float2(__uint_as_float(this->w[j] << 16), __uint_as_float(this->w[j] & 0xffff0000u));
+    }
+};
+template <int NS>
+struct StateVec<__half, NS> : StateVecHalf<__half, NS> {
+    __device__ __forceinline__ float2 pair(int j) const {
+        return __half22float2(*reinterpret_cast<const __half2*>(&this->w[j]));
+    }
 };
 
 // Plain-load path for one tile (used when a tensor breaks a TMA layout rule).
@@ -88,10 +143,12 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     constexpr bool kSoftplus = (FLAGS & 1) != 0, kGate = (FLAGS & 2) != 0, kConv = (FLAGS & 4) != 0;
     constexpr int NS = Tr::NS, LPC = Tr::LPC, TC = Tr::TC, DT = Tr::DT, NP = Tr::NP,
                   THREADS = Tr::THREADS, STAGES = Tr::STAGES;
-    constexpr int RB = 4;  // timesteps whose elementwise work is done ahead of the recurrence
+    constexpr int RB = Tr::RB, OWN = Tr::OWN;
+    constexpr bool SHARE = Tr::SHARE;
     extern __shared__ __align__(128) unsigned char smem[];
-    float* Bs = reinterpret_cast<float*>(smem + Tr::OFF_BS);
-    float* Cs = reinterpret_cast<float*>(smem + Tr::OFF_CS);
+    Tact* Bs = reinterpret_cast<Tact*>(smem + Tr::OFF_BS);
+    Tact* Cs = reinterpret_cast<Tact*>(smem + Tr::OFF_CS);
+    float* halo = reinterpret_cast<float*>(smem + Tr::OFF_HALO);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Tr::OFF_BAR);
 
     const int tid = threadIdx.x;
@@ -189,19 +246,25 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     const float a2_mid = a2[NS / 4].x;  // second seed of the power chain (NS == 16)
     (void)a2_mid;
     const float Dd = d_ok ? p.Dp[d] : 0.0f;
-    // conv taps and the sliding window (oldest -> newest), right-aligned:
-    // tap k of K sits at index kKMax-K+k.
-    float cw[kKMax], win[kKMax];
+    // conv taps in registers; the window of the K most recent x values per
+    // channel (oldest -> newest) lives in shared memory between chunks.
+    float cw[kKMax];
     float cb = 0.0f;
 #pragma unroll
-    for (int k = 0; k < kKMax; ++k) {
-        const int kk = k - (kKMax - K);
-        cw[k] = (kk >= 0 && d_ok) ? p.conv_w[static_cast<long long>(d) * K + kk] : 0.0f;
-        win[k] = (kk >= 0 && d_ok && p.conv_state)
-                     ? p.conv_state[(static_cast<long long>(b) * D + d) * K + kk]
-                     : 0.0f;
-    }
+    for (int k = 0; k < kKMax; ++k)
+        cw[k] = (k < K && d_ok) ? p.conv_w[static_cast<long long>(d) * K + k] : 0.0f;
     if (K && d_ok) cb = p.conv_b[d];
+    if (kConv) {
+        for (int i = tid; i < kKMax * DT; i += THREADS) {
+            const int k = i / DT, cc = i - k * DT;
+            float hv = 0.0f;
+            if (k < K && d0 + cc < D && p.conv_state)
+                hv = p.conv_state[(static_cast<long long>(b) * D + d0 + cc) * K + k];
+            halo[i] = hv;
+        }
+        __syncthreads();
+    }
+    const int lane_base = (tid & 31) & ~(LPC - 1);  // lane holding slice 0 of this channel
 
     const long long save_chunks = p.chunk_states ? (T + p.save_stride - 1) / p.save_stride : 0;
 
@@ -232,21 +295,29 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!(load_mask & kTmaC))
                 load_tile_plain(raw_c(s), static_cast<const Tact*>(p.cm), p.ld_bc, b, T, t0, 0, N,
                                 TC, N, THREADS);
-            __syncthreads();
         }
+        // the y buffer written in this iteration was last stored two chunks ago:
+        // wait until that bulk store has finished reading it (one store may stay
+        // in flight); the barrier that follows orders this before any write.
+        if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         if (tx_bytes) mbar_wait(&bars[s], (c / STAGES) & 1, p.status);
+        __syncthreads();
 
-        // B / C of the chunk -> f32, zero-padded to NP columns (shared by the CTA).
-        {
+        // B / C are read by the recurrence straight from the landed tile in their
+        // storage dtype (half the shared-memory traffic of an f32 copy).  Only a
+        // d_state that is not a whole number of lane slices needs a zero-padded copy.
+        const bool padded = N != NP;
+        if (padded) {
             const Tact* rb = raw_b(s);
             const Tact* rc = raw_c(s);
+            const Tact zero = from_f<Tact>(0.0f);
             for (int i = tid; i < TC * NP; i += THREADS) {
                 const int r = i / NP, n = i - r * NP;
-                Bs[i] = n < N ? to_f(rb[r * N + n]) : 0.0f;
-                Cs[i] = n < N ? to_f(rc[r * N + n]) : 0.0f;
+                Bs[i] = n < N ? rb[r * N + n] : zero;
+                Cs[i] = n < N ? rc[r * N + n] : zero;
             }
+            __syncthreads();
         }
-        __syncthreads();
 
         // Training save: state entering each block of save_stride steps.
         if (p.chunk_states && (t0 % p.save_stride) == 0) {
@@ -263,24 +334,31 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         const Tact* rx = raw_x(s) + col;
         const Tact* rd = raw_dl(s) + col;
         const Tact* rz = raw_z(s) + col;
+        const float* hl = halo + col;
         Tact* ot = out_tile(c & 1) + col;
-        const float* Bp = Bs + n0;
-        const float* Cp = Cs + n0;
+        const Tact* Bp = (padded ? Bs : raw_b(s)) + n0;
+        const Tact* Cp = (padded ? Cs : raw_c(s)) + n0;
 
         // Elementwise stage of one timestep (row r of the chunk).
         auto elem = [&](int r) -> Elem {
-            float u = to_f(rx[r * DT]);
+            float u;
             if (kConv) {
-#pragma unroll
-                for (int k = 0; k < kKMax - 1; ++k) win[k] = win[k + 1];
-                win[kKMax - 1] = u;
                 float acc = cb;
 #pragma unroll
-                for (int k = 0; k < kKMax; ++k) acc = fmaf(win[k], cw[k], acc);
+                for (int k = 0; k < kKMax; ++k) {
+                    // tap k reads x[r - (K-1) + k]: this chunk's tile, or the window
+                    // carried from the previous chunk for the first K-1 rows.
+                    const int rr = r - (K - 1) + k;
+                    const float a = to_f(rx[max(rr, 0) * DT]);
+                    const float w = hl[min(max(K + rr, 0), kKMax - 1) * DT];
+                    acc = fmaf(rr >= 0 ? a : w, cw[k], acc);  // cw[k] == 0 for k >= K
+                }
                 u = siluf_fast(acc);
-                if (p.u_out && d_ok && part == 0)
+                if (p.u_out && d_ok)
                     static_cast<Tact*>(p.u_out)[(static_cast<long long>(b) * T + t0 + r) * p.ld_u + d] =
                         from_f<Tact>(u);
+            } else {
+                u = to_f(rx[r * DT]);
             }
             float dv = to_f(rd[r * DT]);
             if (kSoftplus) dv = softplusf_fast(dv);
@@ -297,31 +375,42 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             o.sk = Dd * u * gv;
             return o;
         };
+        // Elementwise work this lane owns in the block starting at row r0.
+        auto elem_block = [&](int r0, Elem* out) {
+#pragma unroll
+            for (int k = 0; k < OWN; ++k) out[k] = elem(SHARE ? r0 + k * LPC + part : r0 + k);
+        };
 
-        // Recurrence of NB timesteps starting at row r0; B/C of the whole block are
-        // fetched first so that their latency overlaps the arithmetic.
+        // Recurrence of the block at row r0 (NB = RB), or of the single row r0
+        // (NB = 1, ragged last chunk; `el` then holds that row for every lane).
         auto recur = [&](auto geo_tag, auto nb_tag, int r0, const Elem* el) {
             constexpr bool GEO = decltype(geo_tag)::value;
             constexpr int NB = decltype(nb_tag)::value;
-            float4 Bq[NB][NS / 4], Cq[NB][NS / 4];
+            constexpr bool SH = SHARE && NB == RB;
+            StateVec<Tact, NS> Bq[NB], Cq[NB];
 #pragma unroll
-            for (int i = 0; i < NB; ++i)
-#pragma unroll
-                for (int j = 0; j < NS / 4; ++j) {
-                    Bq[i][j] = *reinterpret_cast<const float4*>(Bp + (r0 + i) * NP + 4 * j);
-                    Cq[i][j] = *reinterpret_cast<const float4*>(Cp + (r0 + i) * NP + 4 * j);
-                }
+            for (int i = 0; i < NB; ++i) {
+                Bq[i].load(Bp + (r0 + i) * NP);
+                Cq[i].load(Cp + (r0 + i) * NP);
+            }
             float yo[NB];
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
+                // (delta, delta*u) of row i: from the lane that owns the row
+                const int k = SH ? i / LPC : i;
+                float dli = el[k].dl, dui = el[k].du;
+                if (SH) {
+                    dli = __shfl_sync(0xffffffffu, dli, lane_base + (i % LPC));
+                    dui = __shfl_sync(0xffffffffu, dui, lane_base + (i % LPC));
+                }
                 float2 e[NS / 2];
                 if (GEO) {
                     // e[j] = (E R^(2j), E R^(2j+1)): product tree of depth <= 3,
                     // re-seeded at the middle state when NS == 16.
-                    const float R = ex2(el[i].dl * a2_step);
+                    const float R = ex2(dli * a2_step);
                     const float R2 = R * R;
                     const float2 r2 = splat2(R2), r4 = splat2(R2 * R2);
-                    const float E0 = ex2(el[i].dl * a2_first);
+                    const float E0 = ex2(dli * a2_first);
                     e[0] = make_float2(E0, E0 * R);
                     e[1] = mul2(e[0], r2);
                     if (NS >= 8) {
@@ -329,71 +418,65 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                         e[3] = mul2(e[1], r4);
                     }
                     if (NS == 16) {
-                        const float E1 = ex2(el[i].dl * a2_mid);
+                        const float E1 = ex2(dli * a2_mid);
                         e[4] = make_float2(E1, E1 * R);
                         e[5] = mul2(e[4], r2);
                         e[6] = mul2(e[4], r4);
                         e[7] = mul2(e[5], r4);
                     }
                 } else {
-                    const float2 dl2 = splat2(el[i].dl);
+                    const float2 dl2 = splat2(dli);
 #pragma unroll
                     for (int j = 0; j < NS / 2; ++j) {
                         const float2 xa = mul2(dl2, a2[j]);
                         e[j] = make_float2(ex2(xa.x), ex2(xa.y));
                     }
                 }
-                const float2 du2 = splat2(el[i].du);
+                const float2 du2 = splat2(dui);
                 float2 dub[NS / 2];
 #pragma unroll
-                for (int j = 0; j < NS / 4; ++j) {
-                    dub[2 * j] = mul2(du2, make_float2(Bq[i][j].x, Bq[i][j].y));
-                    dub[2 * j + 1] = mul2(du2, make_float2(Bq[i][j].z, Bq[i][j].w));
-                }
+                for (int j = 0; j < NS / 2; ++j) dub[j] = mul2(du2, Bq[i].pair(j));
 #pragma unroll
                 for (int j = 0; j < NS / 2; ++j) h[j] = fma2(e[j], h[j], dub[j]);
-                float2 yp[NS / 2];
+                // y = <h, C>: two independent fma chains
+                float2 ya = mul2(h[0], Cq[i].pair(0));
+                float2 yb = mul2(h[1], Cq[i].pair(1));
 #pragma unroll
-                for (int j = 0; j < NS / 4; ++j) {
-                    yp[2 * j] = mul2(h[2 * j], make_float2(Cq[i][j].x, Cq[i][j].y));
-                    yp[2 * j + 1] = mul2(h[2 * j + 1], make_float2(Cq[i][j].z, Cq[i][j].w));
+                for (int j = 1; j < NS / 4; ++j) {
+                    ya = fma2(h[2 * j], Cq[i].pair(2 * j), ya);
+                    yb = fma2(h[2 * j + 1], Cq[i].pair(2 * j + 1), yb);
                 }
-#pragma unroll
-                for (int w = NS / 4; w >= 1; w >>= 1)
-#pragma unroll
-                    for (int j = 0; j < w; ++j) yp[j] = add2(yp[j], yp[j + w]);
-                float y = yp[0].x + yp[0].y;
+                const float2 y2 = add2(ya, yb);
+                float y = y2.x + y2.y;
 #pragma unroll
                 for (int m = 1; m < LPC; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
-                yo[i] = fmaf(y, el[i].g, el[i].sk);
+                // gate and skip are applied by the lane that owns the row
+                yo[i] = fmaf(y, el[k].g, el[k].sk);
             }
             // Stores after every load of the block.
-            if (part == 0) {
 #pragma unroll
-                for (int i = 0; i < NB; ++i) ot[(r0 + i) * DT] = from_f<Tact>(yo[i]);
-            }
+            for (int i = 0; i < NB; ++i)
+                if (part == (SH ? i % LPC : 0)) ot[(r0 + i) * DT] = from_f<Tact>(yo[i]);
         };
         auto run = [&](auto geo_tag) {
             if (nv == TC) {
-                Elem cur[RB], nxt[RB];
-#pragma unroll
-                for (int i = 0; i < RB; ++i) cur[i] = elem(i);
+                Elem cur[OWN], nxt[OWN];
+                elem_block(0, cur);
                 // Every iteration but the last also does the elementwise work of the
                 // following block; it is independent of this block's recurrence and
                 // sits in the same basic block, so the two interleave.
 #pragma unroll 1
                 for (int r0 = 0; r0 < TC - RB; r0 += RB) {
-#pragma unroll
-                    for (int i = 0; i < RB; ++i) nxt[i] = elem(r0 + RB + i);
+                    elem_block(r0 + RB, nxt);
                     recur(geo_tag, std::integral_constant<int, RB>{}, r0, cur);
 #pragma unroll
-                    for (int i = 0; i < RB; ++i) cur[i] = nxt[i];
+                    for (int k = 0; k < OWN; ++k) cur[k] = nxt[k];
                 }
                 recur(geo_tag, std::integral_constant<int, RB>{}, TC - RB, cur);
             } else {
 #pragma unroll 1
                 for (int r0 = 0; r0 < nv; ++r0) {
-                    Elem one = elem(r0);
+                    Elem one = elem(r0);  // every lane: no sharing on the ragged tail
                     recur(geo_tag, std::integral_constant<int, 1>{}, r0, &one);
                 }
             }
@@ -408,8 +491,6 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (tid == 0) {
                 tma_store_3d(&p.tm_y, out_tile(c & 1), d0, t0, b);
                 tma_commit();
-                // the other y buffer (written next) must have been fully read
-                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             }
         } else {
             __syncthreads();
@@ -420,6 +501,25 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                 if (d0 + cidx < D)
                     yb[(static_cast<long long>(b) * T + t0 + r) * p.ld_y + d0 + cidx] = o[i];
             }
+        }
+        // Conv window hand-over: the K most recent x values per channel.  Readers
+        // of the old window finished before the barrier above; the next chunk's
+        // first read comes after its own barrier.
+        if (kConv) {
+            const Tact* rxs = raw_x(s);
+            for (int i = tid; i < DT; i += THREADS) {
+                float nw[kKMax];
+#pragma unroll
+                for (int k = 0; k < kKMax; ++k) {
+                    const int rr = nv - K + k;  // row of this chunk, or negative: old window
+                    nw[k] = (k < K) ? (rr >= 0 ? to_f(rxs[max(rr, 0) * DT + i])
+                                               : halo[min(max(K + rr, 0), kKMax - 1) * DT + i])
+                                    : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < kKMax; ++k) halo[k * DT + i] = nw[k];
+            }
+            __syncthreads();  // the window is read by other threads in the next chunk
         }
     }
 
@@ -433,9 +533,12 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                     (j & 1) ? h[j / 2].y : h[j / 2].x;
         }
     }
-    if (K && p.conv_state && d_ok && part == 0) {
-        for (int k = 0; k < K; ++k)
-            p.conv_state[(static_cast<long long>(b) * D + d) * K + k] = win[kKMax - K + k];
+    if (kConv && p.conv_state) {
+        __syncthreads();
+        for (int i = tid; i < DT; i += THREADS)
+            if (d0 + i < D)
+                for (int k = 0; k < K; ++k)
+                    p.conv_state[(static_cast<long long>(b) * D + d0 + i) * K + k] = halo[k * DT + i];
     }
     if (tid == 0) tma_wait_read0();  // shared memory must outlive the last bulk store
 }
@@ -449,7 +552,7 @@ struct FwdVariant {
 };
 
 #ifndef MB200_FWD_WARPS
-#define MB200_FWD_WARPS 2
+#define MB200_FWD_WARPS 4
 #endif
 #ifndef MB200_FWD_TC
 #define MB200_FWD_TC 16
@@ -484,10 +587,10 @@ static int build_fwd_variants(FwdVariant* v) {
     v[n++] = make_variant<Tact, 4, 1>();
     v[n++] = make_variant<Tact, 8, 1>();
 #endif
-#ifdef MB200_FWD_NS8X2
-    v[n++] = make_variant<Tact, 8, 2>();
-#else
+#ifdef MB200_FWD_NS16
     v[n++] = make_variant<Tact, 16, 1>();
+#else
+    v[n++] = make_variant<Tact, 8, 2>();
 #endif
 #ifndef MB200_FWD_TUNING
     v[n++] = make_variant<Tact, 16, 2>();
