@@ -115,6 +115,134 @@ MAMBA_B200_API int mamba_b200_ssm_scan_fwd_nosave(void* handle, void* stream, in
                                    const void* C, const float* a_neg, const float* D, int batch,
                                    int T, int d_inner, int d_state);
 
+/*
+ * Mamba-1 fused backward (BPTT) by recomputation.  One call replaces, per layer,
+ * gating_backward_{dt} (kernels/elementwise.cu:191-233), the B/C gather,
+ * ssm_parallel_scan_bwd_{dt} / ssm_backward_local_{dt}
+ * (kernels/mamba_ssm_parallel.cu:1182-1532, kernels/mamba_ssm.cu:466-662), the four
+ * reducers ssm_reduce_d_{B,C,D,a_log} (kernels/mamba_ssm.cu:667-763) and
+ * softplus_backward (kernels/activations.cu:68-104); launch sites
+ * src/mamba_ssm/gpu/backward_mixed.rs:162-425.  It reads the block-boundary
+ * states the training-mode forward saved (chunk_states) instead of h_saved
+ * [B,(T+1),D,N] and never materialises the [B,T,D,N] dB/dC partials.
+ *   overwritten: d_u, d_delta (w.r.t. the raw input when delta_softplus), d_z
+ *                (storage dtype), dBm, dCm [B,T,N] f32
+ *   accumulated (+=, grad-arena convention of backward_mixed.rs:331-347):
+ *                dA_log [D,N], dD [D] f32
+ * The conv1d backward is a separate entry point because the reference adds the
+ * x_proj GEMM's input gradient to d_u in between (backward_mixed.rs:350-580).
+ */
+typedef struct mamba_b200_sscan_bwd_args {
+    int dtype;
+    int B, T, D, N;        /* N <= 16 */
+    const void* u;         /* [B*T, ld_u] scan input (post conv + SiLU) */
+    long long ld_u;
+    const void* delta;     /* as given to the forward */
+    long long ld_delta;
+    int delta_softplus;
+    const void* Bm;
+    const void* Cm;
+    long long ld_bc;
+    const void* z;
+    long long ld_z;
+    int z_mode;
+    const float* a_neg;
+    const float* Dp;
+    const float* chunk_states; /* [B, ceil(T/save_stride), D, N] from the forward */
+    int save_stride;           /* 16, 32, 48 or 64 */
+    const void* dy;            /* [B*T, ld_dy] gradient w.r.t. the forward output */
+    long long ld_dy;
+    void* d_u;
+    long long ld_du;
+    void* d_delta;
+    long long ld_ddelta;
+    void* d_z;                 /* required when z_mode != 0 */
+    long long ld_dz;
+    float* dBm;                /* [B*T, N] contiguous */
+    float* dCm;
+    float* dA_log;             /* [D, N], += */
+    float* dD;                 /* [D], += */
+    void* workspace;           /* caller-owned scratch, 256-byte aligned */
+    long long workspace_bytes; /* >= mamba_b200_sscan_bwd_workspace_bytes(B,T,D,N) */
+} mamba_b200_sscan_bwd_args;
+
+MAMBA_B200_API long long mamba_b200_sscan_bwd_workspace_bytes(int B, int T, int D, int N);
+MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream, const mamba_b200_sscan_bwd_args* args);
+
+/*
+ * Decode step (T = 1): conv step + SiLU, softplus(delta), SSM step, D skip and
+ * gate in one launch.  Replaces conv1d_step_forward_silu_{dt}
+ * (kernels/conv1d.cu:85-115), softplus_forward_{dt} and
+ * ssm_step_forward_gather_gate_{dt} (kernels/mamba_ssm.cu:180-227); launch sites
+ * src/mamba_ssm/gpu/inference.rs:1062-1215.  Rows are [B, ld]; B and C are
+ * read in place from xdbl.  conv_state / ssm_state are updated in place.
+ */
+typedef struct mamba_b200_sscan_step_args {
+    int dtype;
+    int B, D, N;
+    const void* x;        /* [B, ld_x]: pre-conv x when conv_w != NULL, else u */
+    long long ld_x;
+    const void* delta;    /* [B, ld_delta] */
+    long long ld_delta;
+    int delta_softplus;
+    const void* Bm;       /* [B, ld_bc] */
+    const void* Cm;
+    long long ld_bc;
+    const void* z;        /* [B, ld_z] or NULL */
+    long long ld_z;
+    int z_mode;           /* 0 none, 1 SiLU(z), 2 z is the ready gate */
+    const float* a_neg;
+    const float* Dp;
+    const float* conv_w;  /* [D, K] or NULL */
+    const float* conv_b;
+    float* conv_state;    /* [B, D, K], required with conv_w */
+    int K;
+    float* ssm_state;     /* [B, D, N], required */
+    void* y;              /* [B, ld_y] */
+    long long ld_y;
+    void* u_out;          /* optional [B, ld_u] */
+    long long ld_u;
+} mamba_b200_sscan_step_args;
+
+MAMBA_B200_API int mamba_b200_sscan_step(void* handle, void* stream, const mamba_b200_sscan_step_args* args);
+
+/*
+ * Standalone depthwise causal conv1d + SiLU over a sequence, forward and
+ * backward.  In the layer pipeline u must exist before the x_proj GEMM that
+ * produces B, C and delta, so the conv runs as its own launch ahead of the scan.
+ *   forward : replaces conv1d_burnin_forward[_nosave]_{dt} (kernels/conv1d.cu:161-359;
+ *             src/mamba_ssm/gpu/forward_mixed.rs:500-537, prefill.rs:788); writes u and
+ *             updates conv_state in place.  Nothing is saved for the backward.
+ *   backward: replaces conv1d_burnin_backward_{dt} + two reduce_sum_axis0 launches
+ *             (kernels/conv1d.cu:373-515, backward_mixed.rs:580-659); recomputes the
+ *             pre-activation from x; d_x overwritten, dconv_w / dconv_b accumulated
+ *             (+=) through per-(sample, time chunk) partials added in a fixed order.
+ *             conv_state is the window that ENTERED the forward (NULL = zeros).
+ */
+typedef struct mamba_b200_conv1d_args {
+    int dtype;
+    int B, T, D, K;        /* K = d_conv, 1..8 */
+    const void* x;         /* [B*T, ld_x] pre-conv x branch */
+    long long ld_x;
+    const float* conv_w;   /* [D, K] */
+    const float* conv_b;   /* [D] */
+    float* conv_state;     /* [B, D, K]; forward: in/out (NULL = zeros in, not written) */
+    void* u;               /* forward output [B*T, ld_u] */
+    long long ld_u;
+    const void* d_u;       /* backward: gradient w.r.t. u [B*T, ld_du] */
+    long long ld_du;
+    void* d_x;             /* backward output [B*T, ld_dx] */
+    long long ld_dx;
+    float* dconv_w;        /* [D, K], += */
+    float* dconv_b;        /* [D], += */
+    void* workspace;       /* backward scratch */
+    long long workspace_bytes; /* >= mamba_b200_conv1d_bwd_workspace_bytes(B,T,D,K) */
+} mamba_b200_conv1d_args;
+
+MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream, const mamba_b200_conv1d_args* args);
+MAMBA_B200_API long long mamba_b200_conv1d_bwd_workspace_bytes(int B, int T, int D, int K);
+MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream, const mamba_b200_conv1d_args* args);
+
 #ifdef __cplusplus
 }
 #endif

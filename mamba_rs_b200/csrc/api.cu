@@ -40,6 +40,7 @@ bool make_tmap_3d(Ctx* c, CUtensorMap* map, int dtype, const void* base, long lo
 }
 
 int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limits
+int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
 
 }  // namespace mb200
 
@@ -69,6 +70,8 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     MB200_CUDA_CHECK(c, cudaMalloc(&c->d_status, sizeof(int)));
     MB200_CUDA_CHECK(c, cudaMemset(c->d_status, 0, sizeof(int)));
     int rc = m1_fwd_configure(c);
+    if (rc) return rc;
+    rc = m1_bwd_configure(c);
     if (rc) return rc;
     return MAMBA_B200_OK;
 }

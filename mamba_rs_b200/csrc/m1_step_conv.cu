@@ -1,0 +1,364 @@
+// Decode step (T = 1) and the standalone depthwise causal conv1d kernels.
+//
+// All three are memory-bound streaming kernels: lanes map to consecutive
+// channels so every global access is a contiguous row segment, the conv window
+// lives in registers, and each element of x / u / d_u / d_x is read or written
+// once (plus a K-1 row halo per time chunk).
+#include <string.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace mb200 {
+
+constexpr int kStepKMax = 8;
+
+// ---------------------------------------------------------------------------
+// T = 1: conv step + SiLU, softplus(delta), SSM step, D skip, gate.
+// Replaces conv1d_step_forward_silu_{dt} (kernels/conv1d.cu:85-115), the
+// softplus pass and ssm_step_forward_gather_gate_{dt} (kernels/mamba_ssm.cu:180-227).
+// ---------------------------------------------------------------------------
+struct StepParams {
+    const void *x, *dl, *bm, *cm, *z;
+    void *y, *u_out;
+    long long ld_x, ld_dl, ld_bc, ld_z, ld_y, ld_u;
+    const float *a_neg, *Dp, *conv_w, *conv_b;
+    float *conv_state, *ssm_state;
+    int B, D, N, K, delta_softplus, z_mode;
+};
+
+template <typename Tact>
+__global__ void __launch_bounds__(128) sscan_step_kernel(const StepParams p) {
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= static_cast<long long>(p.B) * p.D) return;
+    const int b = static_cast<int>(idx / p.D), d = static_cast<int>(idx % p.D);
+    const Tact* x = static_cast<const Tact*>(p.x);
+    float u = to_f(x[b * p.ld_x + d]);
+    if (p.conv_w) {
+        // shift, insert, bias-first dot product (kernels/conv1d.cu:100-112)
+        float* st = p.conv_state + (static_cast<long long>(b) * p.D + d) * p.K;
+        float win[kStepKMax];
+        for (int k = 0; k + 1 < p.K; ++k) win[k] = st[k + 1];
+        win[p.K - 1] = u;
+        float acc = p.conv_b[d];
+        for (int k = 0; k < p.K; ++k) {
+            acc = fmaf(win[k], p.conv_w[static_cast<long long>(d) * p.K + k], acc);
+            st[k] = win[k];
+        }
+        u = siluf_fast(acc);
+        if (p.u_out) static_cast<Tact*>(p.u_out)[b * p.ld_u + d] = from_f<Tact>(u);
+    }
+    float dl = to_f(static_cast<const Tact*>(p.dl)[b * p.ld_dl + d]);
+    if (p.delta_softplus) dl = softplusf_fast(dl);
+    const float du = dl * u;
+    const Tact* Bv = static_cast<const Tact*>(p.bm) + b * p.ld_bc;
+    const Tact* Cv = static_cast<const Tact*>(p.cm) + b * p.ld_bc;
+    float* h = p.ssm_state + (static_cast<long long>(b) * p.D + d) * p.N;
+    const float* a = p.a_neg + static_cast<long long>(d) * p.N;
+    float y = 0.0f;
+    int n = 0;
+    if ((p.N & 3) == 0) {
+        for (; n < p.N; n += 4) {
+            float4 hv = *reinterpret_cast<float4*>(h + n);
+            const float4 av = *reinterpret_cast<const float4*>(a + n);
+            hv.x = fmaf(ex2(dl * av.x * kLog2e), hv.x, du * to_f(Bv[n]));
+            hv.y = fmaf(ex2(dl * av.y * kLog2e), hv.y, du * to_f(Bv[n + 1]));
+            hv.z = fmaf(ex2(dl * av.z * kLog2e), hv.z, du * to_f(Bv[n + 2]));
+            hv.w = fmaf(ex2(dl * av.w * kLog2e), hv.w, du * to_f(Bv[n + 3]));
+            y = fmaf(hv.x, to_f(Cv[n]), y);
+            y = fmaf(hv.y, to_f(Cv[n + 1]), y);
+            y = fmaf(hv.z, to_f(Cv[n + 2]), y);
+            y = fmaf(hv.w, to_f(Cv[n + 3]), y);
+            *reinterpret_cast<float4*>(h + n) = hv;
+        }
+    }
+    for (; n < p.N; ++n) {
+        const float hn = fmaf(ex2(dl * a[n] * kLog2e), h[n], du * to_f(Bv[n]));
+        h[n] = hn;
+        y = fmaf(hn, to_f(Cv[n]), y);
+    }
+    y = fmaf(p.Dp[d], u, y);
+    if (p.z_mode) {
+        const float zv = to_f(static_cast<const Tact*>(p.z)[b * p.ld_z + d]);
+        y *= p.z_mode == 1 ? siluf_fast(zv) : zv;
+    }
+    static_cast<Tact*>(p.y)[b * p.ld_y + d] = from_f<Tact>(y);
+}
+
+// ---------------------------------------------------------------------------
+// Sequence conv1d + SiLU forward.  Replaces conv1d_burnin_forward[_nosave]_{dt}
+// (kernels/conv1d.cu:161-359).  grid = (channel tiles, time chunks, B).
+// ---------------------------------------------------------------------------
+constexpr int kConvTT = 64;  // timesteps per thread
+
+struct ConvParams {
+    const void *x, *du;
+    void *u, *dx;
+    long long ld_x, ld_u, ld_du, ld_dx;
+    const float *w, *bias;
+    const float* state_in;  // entering window [B,D,K] or null (zeros)
+    float* state_out;       // window after the sequence [B,D,K] or null (may alias state_in)
+    float* part;            // backward: [B][chunks][D][K+1] partial dW | db
+    int B, T, D, K;
+};
+
+// x[t] for t in [-K, T): negative t reads the entering window (slot K + t).
+template <typename Tact>
+__device__ __forceinline__ float conv_x_at(const ConvParams& p, const Tact* xb, int b, int d, int t) {
+    if (t >= 0) return to_f(xb[static_cast<long long>(t) * p.ld_x]);
+    return p.state_in ? p.state_in[(static_cast<long long>(b) * p.D + d) * p.K + p.K + t] : 0.0f;
+}
+
+template <typename Tact>
+__global__ void __launch_bounds__(128) conv1d_fwd_kernel(const ConvParams p) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = blockIdx.y * kConvTT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const int K = p.K;
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * p.T * p.ld_x + d;
+    Tact* ub = static_cast<Tact*>(p.u) + static_cast<long long>(b) * p.T * p.ld_u + d;
+    float w[kStepKMax], win[kStepKMax];
+#pragma unroll
+    for (int k = 0; k < kStepKMax; ++k) {
+        w[k] = k < K ? p.w[static_cast<long long>(d) * K + k] : 0.0f;
+        // window right-aligned in win[kStepKMax-K .. kStepKMax): history before t0
+        const int kk = k - (kStepKMax - K);
+        win[k] = kk >= 0 ? conv_x_at(p, xb, b, d, t0 - K + kk) : 0.0f;
+    }
+    const float bias = p.bias[d];
+    const int t1 = min(p.T, t0 + kConvTT);
+    for (int t = t0; t < t1; ++t) {
+#pragma unroll
+        for (int k = 0; k < kStepKMax - 1; ++k) win[k] = win[k + 1];
+        win[kStepKMax - 1] = to_f(xb[static_cast<long long>(t) * p.ld_x]);
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < kStepKMax; ++k) {
+            const int kk = k - (kStepKMax - K);
+            if (kk >= 0) acc = fmaf(win[k], w[kk], acc);
+        }
+        ub[static_cast<long long>(t) * p.ld_u] = from_f<Tact>(siluf_fast(acc));
+    }
+}
+
+// Window after the sequence: the last K inputs (older slots come from the
+// entering window when T < K).  Runs after the forward kernel, which reads the
+// entering window, so updating the state in place cannot race with it.
+template <typename Tact>
+__global__ void conv1d_state_kernel(const ConvParams p) {
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= static_cast<long long>(p.B) * p.D) return;
+    const int b = static_cast<int>(idx / p.D), d = static_cast<int>(idx % p.D);
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * p.T * p.ld_x + d;
+    float nw[kStepKMax];
+    for (int k = 0; k < p.K; ++k) nw[k] = conv_x_at(p, xb, b, d, p.T - p.K + k);
+    float* so = p.state_out + (static_cast<long long>(b) * p.D + d) * p.K;
+    for (int k = 0; k < p.K; ++k) so[k] = nw[k];
+}
+
+// ---------------------------------------------------------------------------
+// conv1d + SiLU backward by recomputation.  Replaces conv1d_burnin_backward_{dt}
+// and its two reduce_sum_axis0 launches (kernels/conv1d.cu:373-515,
+// kernels/elementwise.cu:89-114).  d_x[t] = sum_k w[k] dco[t + K-1-k],
+// dco = d_u * SiLU'(conv pre-activation); dW / db partials per (b, time chunk).
+// ---------------------------------------------------------------------------
+template <typename Tact>
+__global__ void __launch_bounds__(128) conv1d_bwd_kernel(const ConvParams p) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    const int chunk = blockIdx.y, t0 = chunk * kConvTT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const int K = p.K, T = p.T;
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * T * p.ld_x + d;
+    const Tact* gb = static_cast<const Tact*>(p.du) + static_cast<long long>(b) * T * p.ld_du + d;
+    Tact* dxb = static_cast<Tact*>(p.dx) + static_cast<long long>(b) * T * p.ld_dx + d;
+    float w[kStepKMax], win[kStepKMax], dco[kStepKMax], dW[kStepKMax];
+#pragma unroll
+    for (int k = 0; k < kStepKMax; ++k) {
+        w[k] = k < K ? p.w[static_cast<long long>(d) * K + k] : 0.0f;
+        dco[k] = 0.0f;
+        dW[k] = 0.0f;
+    }
+    const float bias = p.bias[d];
+    float db = 0.0f;
+    const int t1 = min(T, t0 + kConvTT);
+    // Walk backwards from t1 + K - 2 (future steps whose dco reaches into this
+    // chunk) down to t0.  win holds x[t-K+1 .. t] right-aligned; dco[j] holds
+    // dco[t + j + 1] for the K-1 steps ahead of t.
+    const int t_start = min(T - 1, t1 + K - 2);
+#pragma unroll
+    for (int k = 0; k < kStepKMax; ++k) {
+        const int kk = k - (kStepKMax - K);
+        win[k] = kk >= 0 ? conv_x_at(p, xb, b, d, t_start - (K - 1) + kk) : 0.0f;
+    }
+    for (int t = t_start; t >= t0; --t) {
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < kStepKMax; ++k) {
+            const int kk = k - (kStepKMax - K);
+            if (kk >= 0) acc = fmaf(win[k], w[kk], acc);
+        }
+        const float sg = sigmoidf_fast(acc);
+        const float g = to_f(gb[static_cast<long long>(t) * p.ld_du]) * sg * fmaf(acc, 1.0f - sg, 1.0f);
+        if (t < t1) {
+            db += g;
+            float dx = g * w[K - 1];
+#pragma unroll
+            for (int k = 0; k < kStepKMax; ++k) {
+                const int kk = k - (kStepKMax - K);
+                if (kk >= 0) dW[kk] = fmaf(g, win[k], dW[kk]);
+            }
+            // future steps: dco[j] = dco[t + 1 + j] meets tap K-2-j
+#pragma unroll
+            for (int j = 0; j < kStepKMax - 1; ++j)
+                if (j < K - 1) dx = fmaf(dco[j], w[K - 2 - j], dx);
+            dxb[static_cast<long long>(t) * p.ld_dx] = from_f<Tact>(dx);
+        }
+#pragma unroll
+        for (int j = kStepKMax - 1; j > 0; --j) dco[j] = dco[j - 1];
+        dco[0] = g;
+        // slide the window one step back in time
+#pragma unroll
+        for (int k = kStepKMax - 1; k > 0; --k) win[k] = win[k - 1];
+        win[kStepKMax - K] = conv_x_at(p, xb, b, d, t - K);
+    }
+    const int chunks = gridDim.y;
+    float* pt = p.part + ((static_cast<long long>(b) * chunks + chunk) * p.D + d) * (K + 1);
+    for (int k = 0; k < K; ++k) pt[k] = dW[k];
+    pt[K] = db;
+}
+
+// dW[D,K] += sum over (b, chunk) partials; db[D] likewise, in index order.
+__global__ void conv1d_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dW,
+                                         float* __restrict__ db, int groups, int D, int K) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= D * (K + 1)) return;
+    float acc = 0.0f;
+    for (int g = 0; g < groups; ++g) acc += part[static_cast<long long>(g) * D * (K + 1) + i];
+    const int d = i / (K + 1), k = i % (K + 1);
+    if (k < K) dW[d * K + k] += acc;
+    else db[d] += acc;
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" MAMBA_B200_API int mamba_b200_sscan_step(void* handle, void* stream,
+                                                    const mamba_b200_sscan_step_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "sscan_step: null args");
+    const mamba_b200_sscan_step_args& a = *ap;
+    if (!dtype_ok(a.dtype)) return fail(c, MAMBA_B200_ERR_ARG, "sscan_step: bad dtype %d", a.dtype);
+    if (a.B < 0 || a.D <= 0 || a.N <= 0)
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_step: bad dims B=%d D=%d N=%d", a.B, a.D, a.N);
+    if (a.B == 0) return MAMBA_B200_OK;
+    if (!a.x || !a.delta || !a.Bm || !a.Cm || !a.a_neg || !a.Dp || !a.y || !a.ssm_state)
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_step: null required pointer");
+    if (a.z_mode < 0 || a.z_mode > 2 || (a.z_mode && !a.z))
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_step: z_mode %d needs z", a.z_mode);
+    if (a.conv_w && (!a.conv_b || !a.conv_state || a.K < 1 || a.K > kStepKMax))
+        return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_step: d_conv %d outside 1..%d, or null bias/state", a.K,
+                    kStepKMax);
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = a.x; p.dl = a.delta; p.bm = a.Bm; p.cm = a.Cm; p.z = a.z_mode ? a.z : nullptr;
+    p.y = a.y; p.u_out = a.u_out;
+    p.ld_x = a.ld_x; p.ld_dl = a.ld_delta; p.ld_bc = a.ld_bc; p.ld_z = a.ld_z; p.ld_y = a.ld_y; p.ld_u = a.ld_u;
+    p.a_neg = a.a_neg; p.Dp = a.Dp; p.conv_w = a.conv_w; p.conv_b = a.conv_b;
+    p.conv_state = a.conv_state; p.ssm_state = a.ssm_state;
+    p.B = a.B; p.D = a.D; p.N = a.N; p.K = a.conv_w ? a.K : 0;
+    p.delta_softplus = a.delta_softplus; p.z_mode = a.z_mode;
+    const long long n = static_cast<long long>(a.B) * a.D;
+    const unsigned blocks = static_cast<unsigned>((n + 127) / 128);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a.dtype == MAMBA_B200_F32) sscan_step_kernel<float><<<blocks, 128, 0, st>>>(p);
+    else if (a.dtype == MAMBA_B200_F16) sscan_step_kernel<__half><<<blocks, 128, 0, st>>>(p);
+    else sscan_step_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(p);
+    MB200_CUDA_CHECK(c, cudaGetLastError());
+    return MAMBA_B200_OK;
+}
+
+static int conv_check(Ctx* c, const char* who, const mamba_b200_conv1d_args& a, bool bwd) {
+    if (!dtype_ok(a.dtype)) return fail(c, MAMBA_B200_ERR_ARG, "%s: bad dtype %d", who, a.dtype);
+    if (a.B < 0 || a.T < 0 || a.D <= 0) return fail(c, MAMBA_B200_ERR_ARG, "%s: bad dims", who);
+    if (a.K < 1 || a.K > kStepKMax) return fail(c, MAMBA_B200_ERR_SHAPE, "%s: d_conv %d outside 1..%d", who, a.K, kStepKMax);
+    if (a.B > 65535) return fail(c, MAMBA_B200_ERR_SHAPE, "%s: batch %d > 65535", who, a.B);
+    if (!a.x || !a.conv_w || !a.conv_b) return fail(c, MAMBA_B200_ERR_ARG, "%s: null required pointer", who);
+    if (!bwd && !a.u) return fail(c, MAMBA_B200_ERR_ARG, "%s: null output", who);
+    if (bwd && (!a.d_u || !a.d_x || !a.dconv_w || !a.dconv_b || !a.workspace))
+        return fail(c, MAMBA_B200_ERR_ARG, "%s: null gradient or workspace pointer", who);
+    if (a.ld_x < a.D || (!bwd && a.ld_u < a.D) || (bwd && (a.ld_du < a.D || a.ld_dx < a.D)))
+        return fail(c, MAMBA_B200_ERR_ARG, "%s: a row stride is smaller than its row", who);
+    return MAMBA_B200_OK;
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream,
+                                                    const mamba_b200_conv1d_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "conv1d_fwd: null args");
+    const mamba_b200_conv1d_args& a = *ap;
+    int rc = conv_check(c, "conv1d_fwd", a, false);
+    if (rc) return rc;
+    if (a.B == 0 || a.T == 0) return MAMBA_B200_OK;
+    ConvParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = a.x; p.u = a.u; p.ld_x = a.ld_x; p.ld_u = a.ld_u; p.w = a.conv_w; p.bias = a.conv_b;
+    p.state_in = a.conv_state; p.state_out = a.conv_state;
+    p.B = a.B; p.T = a.T; p.D = a.D; p.K = a.K;
+    const int chunks = (a.T + kConvTT - 1) / kConvTT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((a.D + 127) / 128, chunks, a.B);
+    const unsigned sb = static_cast<unsigned>((static_cast<long long>(a.B) * a.D + 127) / 128);
+    if (a.dtype == MAMBA_B200_F32) {
+        conv1d_fwd_kernel<float><<<grid, 128, 0, st>>>(p);
+        if (a.conv_state) conv1d_state_kernel<float><<<sb, 128, 0, st>>>(p);
+    } else if (a.dtype == MAMBA_B200_F16) {
+        conv1d_fwd_kernel<__half><<<grid, 128, 0, st>>>(p);
+        if (a.conv_state) conv1d_state_kernel<__half><<<sb, 128, 0, st>>>(p);
+    } else {
+        conv1d_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+        if (a.conv_state) conv1d_state_kernel<__nv_bfloat16><<<sb, 128, 0, st>>>(p);
+    }
+    MB200_CUDA_CHECK(c, cudaGetLastError());
+    return MAMBA_B200_OK;
+}
+
+extern "C" MAMBA_B200_API long long mamba_b200_conv1d_bwd_workspace_bytes(int B, int T, int D, int K) {
+    if (B <= 0 || T <= 0 || D <= 0 || K <= 0) return 0;
+    const long long chunks = (T + kConvTT - 1) / kConvTT;
+    return static_cast<long long>(sizeof(float)) * B * chunks * D * (K + 1);
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
+                                                    const mamba_b200_conv1d_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "conv1d_bwd: null args");
+    const mamba_b200_conv1d_args& a = *ap;
+    int rc = conv_check(c, "conv1d_bwd", a, true);
+    if (rc) return rc;
+    if (a.B == 0 || a.T == 0) return MAMBA_B200_OK;
+    const int chunks = (a.T + kConvTT - 1) / kConvTT;
+    const long long need = static_cast<long long>(sizeof(float)) * a.B * chunks * a.D * (a.K + 1);
+    if (a.workspace_bytes < need)
+        return fail(c, MAMBA_B200_ERR_ARG, "conv1d_bwd: workspace %lld < %lld bytes", a.workspace_bytes, need);
+    ConvParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = a.x; p.du = a.d_u; p.dx = a.d_x; p.ld_x = a.ld_x; p.ld_du = a.ld_du; p.ld_dx = a.ld_dx;
+    p.w = a.conv_w; p.bias = a.conv_b; p.state_in = a.conv_state;
+    p.part = static_cast<float*>(a.workspace);
+    p.B = a.B; p.T = a.T; p.D = a.D; p.K = a.K;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((a.D + 127) / 128, chunks, a.B);
+    if (a.dtype == MAMBA_B200_F32) conv1d_bwd_kernel<float><<<grid, 128, 0, st>>>(p);
+    else if (a.dtype == MAMBA_B200_F16) conv1d_bwd_kernel<__half><<<grid, 128, 0, st>>>(p);
+    else conv1d_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+    MB200_CUDA_CHECK(c, cudaGetLastError());
+    const int n = a.D * (a.K + 1);
+    conv1d_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(p.part, a.dconv_w, a.dconv_b, a.B * chunks,
+                                                             a.D, a.K);
+    MB200_CUDA_CHECK(c, cudaGetLastError());
+    return MAMBA_B200_OK;
+}

@@ -36,6 +36,52 @@ class SscanFwdArgs(C.Structure):
     ]
 
 
+class SscanBwdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("T", C.c_int), ("D", C.c_int), ("N", C.c_int),
+        ("u", C.c_void_p), ("ld_u", C.c_longlong),
+        ("delta", C.c_void_p), ("ld_delta", C.c_longlong), ("delta_softplus", C.c_int),
+        ("Bm", C.c_void_p), ("Cm", C.c_void_p), ("ld_bc", C.c_longlong),
+        ("z", C.c_void_p), ("ld_z", C.c_longlong), ("z_mode", C.c_int),
+        ("a_neg", C.c_void_p), ("Dp", C.c_void_p),
+        ("chunk_states", C.c_void_p), ("save_stride", C.c_int),
+        ("dy", C.c_void_p), ("ld_dy", C.c_longlong),
+        ("d_u", C.c_void_p), ("ld_du", C.c_longlong),
+        ("d_delta", C.c_void_p), ("ld_ddelta", C.c_longlong),
+        ("d_z", C.c_void_p), ("ld_dz", C.c_longlong),
+        ("dBm", C.c_void_p), ("dCm", C.c_void_p), ("dA_log", C.c_void_p), ("dD", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong),
+    ]
+
+
+class SscanStepArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("D", C.c_int), ("N", C.c_int),
+        ("x", C.c_void_p), ("ld_x", C.c_longlong),
+        ("delta", C.c_void_p), ("ld_delta", C.c_longlong), ("delta_softplus", C.c_int),
+        ("Bm", C.c_void_p), ("Cm", C.c_void_p), ("ld_bc", C.c_longlong),
+        ("z", C.c_void_p), ("ld_z", C.c_longlong), ("z_mode", C.c_int),
+        ("a_neg", C.c_void_p), ("Dp", C.c_void_p),
+        ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("conv_state", C.c_void_p), ("K", C.c_int),
+        ("ssm_state", C.c_void_p),
+        ("y", C.c_void_p), ("ld_y", C.c_longlong),
+        ("u_out", C.c_void_p), ("ld_u", C.c_longlong),
+    ]
+
+
+class Conv1dArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("T", C.c_int), ("D", C.c_int), ("K", C.c_int),
+        ("x", C.c_void_p), ("ld_x", C.c_longlong),
+        ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("conv_state", C.c_void_p),
+        ("u", C.c_void_p), ("ld_u", C.c_longlong),
+        ("d_u", C.c_void_p), ("ld_du", C.c_longlong),
+        ("d_x", C.c_void_p), ("ld_dx", C.c_longlong),
+        ("dconv_w", C.c_void_p), ("dconv_b", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong),
+    ]
+
+
 _lib = None
 
 
@@ -54,6 +100,14 @@ def lib() -> C.CDLL:
         _lib.mamba_b200_destroy.argtypes = [C.c_void_p]
         _lib.mamba_b200_check_status.argtypes = [C.c_void_p, C.c_void_p]
         _lib.mamba_b200_sscan_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanFwdArgs)]
+        _lib.mamba_b200_sscan_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanBwdArgs)]
+        _lib.mamba_b200_sscan_step.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanStepArgs)]
+        _lib.mamba_b200_conv1d_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]
+        _lib.mamba_b200_conv1d_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]
+        _lib.mamba_b200_conv1d_bwd_workspace_bytes.restype = C.c_longlong
+        _lib.mamba_b200_conv1d_bwd_workspace_bytes.argtypes = [C.c_int] * 4
+        _lib.mamba_b200_sscan_bwd_workspace_bytes.restype = C.c_longlong
+        _lib.mamba_b200_sscan_bwd_workspace_bytes.argtypes = [C.c_int] * 4
     return _lib
 
 

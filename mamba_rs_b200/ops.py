@@ -15,7 +15,8 @@ import torch
 
 from . import ffi
 
-__all__ = ["selective_scan_fwd", "ssm_parallel_scan_fwd_nosave", "dtype_code"]
+__all__ = ["selective_scan_fwd", "selective_scan_bwd", "selective_scan_bwd_workspace_bytes",
+           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "dtype_code"]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -115,3 +116,137 @@ def ssm_parallel_scan_fwd_nosave(h_state, y_out, delta, u, Bm, Cm, a_neg, Dp, *,
                 C.c_int(T), C.c_int(D), C.c_int(N))
     hd.check(rc, "mamba_b200_ssm_scan_fwd_nosave")
     return y_out
+
+
+def selective_scan_bwd_workspace_bytes(B, T, D, N) -> int:
+    """Bytes of caller-owned scratch the backward needs (per-tile dB/dC partials
+    and per-sample dA_log / dD partials)."""
+    return int(ffi.lib().mamba_b200_sscan_bwd_workspace_bytes(B, T, D, N))
+
+
+def selective_scan_bwd(u, delta, Bm, Cm, a_neg, Dp, dy, chunk_states, save_stride, z=None, *,
+                       z_mode=None, delta_softplus=True, dA_log=None, dD=None, workspace=None,
+                       handle=None):
+    """Fused backward (BPTT by recomputation from the saved block-boundary
+    states).  Returns dict(d_u, d_delta, d_z, dB, dC, dA_log, dD); dA_log and
+    dD are accumulated into the tensors passed in (zeros if none are passed)."""
+    _require_cuda(u, delta, Bm, Cm, a_neg, Dp, dy, chunk_states, z)
+    Bsz, T, D = delta.shape
+    N = a_neg.shape[1]
+    dev = u.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    if z_mode is None:
+        z_mode = 0 if z is None else 1
+    f32 = dict(dtype=torch.float32, device=dev)
+    d_u = torch.empty((Bsz, T, D), dtype=u.dtype, device=dev)
+    d_delta = torch.empty((Bsz, T, D), dtype=u.dtype, device=dev)
+    d_z = torch.empty((Bsz, T, D), dtype=u.dtype, device=dev) if z_mode else None
+    dB = torch.empty((Bsz, T, N), **f32)
+    dC = torch.empty((Bsz, T, N), **f32)
+    dA_log = torch.zeros((D, N), **f32) if dA_log is None else dA_log
+    dD = torch.zeros((D,), **f32) if dD is None else dD
+    need = selective_scan_bwd_workspace_bytes(Bsz, T, D, N)
+    if workspace is None:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+    a = ffi.SscanBwdArgs()
+    a.dtype = dtype_code(u.dtype)
+    a.B, a.T, a.D, a.N = Bsz, T, D, N
+    a.u, a.ld_u = _ptr(u), _rows(u, "u")
+    a.delta, a.ld_delta, a.delta_softplus = _ptr(delta), _rows(delta, "delta"), int(delta_softplus)
+    a.Bm, a.Cm, a.ld_bc = _ptr(Bm), _ptr(Cm), _rows(Bm, "B")
+    a.z, a.ld_z, a.z_mode = _ptr(z), (_rows(z, "z") if z is not None else 0), int(z_mode)
+    a.a_neg, a.Dp = _ptr(a_neg), _ptr(Dp)
+    a.chunk_states, a.save_stride = _ptr(chunk_states), int(save_stride)
+    a.dy, a.ld_dy = _ptr(dy), _rows(dy, "dy")
+    a.d_u, a.ld_du = _ptr(d_u), D
+    a.d_delta, a.ld_ddelta = _ptr(d_delta), D
+    a.d_z, a.ld_dz = _ptr(d_z), D
+    a.dBm, a.dCm, a.dA_log, a.dD = _ptr(dB), _ptr(dC), _ptr(dA_log), _ptr(dD)
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_sscan_bwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_sscan_bwd")
+    return dict(d_u=d_u, d_delta=d_delta, d_z=d_z, dB=dB, dC=dC, dA_log=dA_log, dD=dD)
+
+
+def selective_scan_step(x, delta, Bm, Cm, a_neg, Dp, ssm_state, z=None, *, z_mode=None,
+                        delta_softplus=True, conv_w=None, conv_b=None, conv_state=None, y=None,
+                        u_out=None, handle=None):
+    """T = 1 decode step (GpuMambaBackbone::step inner kernels).  x, delta, z:
+    [B,D]; Bm, Cm: [B,N] (views of xdbl are fine); states updated in place."""
+    _require_cuda(x, delta, Bm, Cm, a_neg, Dp, ssm_state, z, conv_w, conv_b, conv_state)
+    Bsz, D = delta.shape
+    N = a_neg.shape[1]
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    if y is None:
+        y = torch.empty((Bsz, D), dtype=x.dtype, device=dev)
+    if z_mode is None:
+        z_mode = 0 if z is None else 1
+    a = ffi.SscanStepArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.D, a.N = Bsz, D, N
+    a.x, a.ld_x = _ptr(x), x.stride(0)
+    a.delta, a.ld_delta, a.delta_softplus = _ptr(delta), delta.stride(0), int(delta_softplus)
+    a.Bm, a.Cm, a.ld_bc = _ptr(Bm), _ptr(Cm), Bm.stride(0)
+    a.z, a.ld_z, a.z_mode = _ptr(z), (z.stride(0) if z is not None else 0), int(z_mode)
+    a.a_neg, a.Dp = _ptr(a_neg), _ptr(Dp)
+    a.conv_w, a.conv_b, a.conv_state = _ptr(conv_w), _ptr(conv_b), _ptr(conv_state)
+    a.K = conv_w.shape[1] if conv_w is not None else 0
+    a.ssm_state = _ptr(ssm_state)
+    a.y, a.ld_y = _ptr(y), y.stride(0)
+    a.u_out, a.ld_u = _ptr(u_out), (u_out.stride(0) if u_out is not None else 0)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_sscan_step(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_sscan_step")
+    return y
+
+
+def conv1d_fwd(x, conv_w, conv_b, conv_state=None, u=None, *, handle=None):
+    """Depthwise causal conv1d + SiLU over [B,T,D]; conv_state [B,D,K] in/out."""
+    _require_cuda(x, conv_w, conv_b, conv_state, u)
+    Bsz, T, D = x.shape
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    if u is None:
+        u = torch.empty((Bsz, T, D), dtype=x.dtype, device=dev)
+    a = ffi.Conv1dArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.T, a.D, a.K = Bsz, T, D, conv_w.shape[1]
+    a.x, a.ld_x = _ptr(x), _rows(x, "x")
+    a.conv_w, a.conv_b, a.conv_state = _ptr(conv_w), _ptr(conv_b), _ptr(conv_state)
+    a.u, a.ld_u = _ptr(u), _rows(u, "u")
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_conv1d_fwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_conv1d_fwd")
+    return u
+
+
+def conv1d_bwd(x, conv_w, conv_b, d_u, conv_state0=None, *, dconv_w=None, dconv_b=None,
+               workspace=None, handle=None):
+    """Backward of conv1d + SiLU by recomputation.  Returns dict(d_x, dconv_w,
+    dconv_b); the parameter gradients are accumulated into the tensors given."""
+    _require_cuda(x, conv_w, conv_b, d_u, conv_state0)
+    Bsz, T, D = x.shape
+    K = conv_w.shape[1]
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    d_x = torch.empty((Bsz, T, D), dtype=x.dtype, device=dev)
+    dconv_w = torch.zeros((D, K), dtype=torch.float32, device=dev) if dconv_w is None else dconv_w
+    dconv_b = torch.zeros((D,), dtype=torch.float32, device=dev) if dconv_b is None else dconv_b
+    need = int(ffi.lib().mamba_b200_conv1d_bwd_workspace_bytes(Bsz, T, D, K))
+    if workspace is None:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+    a = ffi.Conv1dArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.T, a.D, a.K = Bsz, T, D, K
+    a.x, a.ld_x = _ptr(x), _rows(x, "x")
+    a.conv_w, a.conv_b, a.conv_state = _ptr(conv_w), _ptr(conv_b), _ptr(conv_state0)
+    a.d_u, a.ld_du = _ptr(d_u), _rows(d_u, "d_u")
+    a.d_x, a.ld_dx = _ptr(d_x), D
+    a.dconv_w, a.dconv_b = _ptr(dconv_w), _ptr(dconv_b)
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_conv1d_bwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_conv1d_bwd")
+    return dict(d_x=d_x, dconv_w=dconv_w, dconv_b=dconv_b)

@@ -278,3 +278,27 @@ def det_rand(n: int, seed: int) -> np.ndarray:
         s ^= (s << 5) & 0xFFFFFFFF
         out[i] = np.float32(s & 0xFFFF) / np.float32(65536.0) - np.float32(0.5)
     return out
+
+
+def conv1d_fwd(x, w, bias, conv_state=None):
+    """Standalone conv1d + SiLU.  x [B,T,D]; returns dict(u, conv_state)."""
+    x, w, bias = _f32(x), _f32(w), _f32(bias)
+    B, T, D = x.shape
+    K = w.shape[1]
+    cst = np.zeros((B, D, K), np.float32) if conv_state is None else _f32(conv_state).copy()
+    u = np.empty((B, T, D), np.float32)
+    lib().orc_conv1d_fwd(B, T, D, K, _p(x), C.c_long(D), _p(w), _p(bias), _p(cst), _p(u))
+    return dict(u=u, conv_state=cst)
+
+
+def conv1d_bwd(x, w, bias, d_u, conv_state0=None):
+    """Backward of conv1d + SiLU.  Returns dict(d_x, dconv_w, dconv_b)."""
+    x, w, bias, d_u, conv_state0 = map(_f32, (x, w, bias, d_u, conv_state0))
+    B, T, D = x.shape
+    K = w.shape[1]
+    d_x = np.empty((B, T, D), np.float32)
+    dW = np.zeros((D, K), np.float32)
+    db = np.zeros((D,), np.float32)
+    lib().orc_conv1d_bwd(B, T, D, K, _p(x), C.c_long(D), _p(w), _p(bias), _p(conv_state0), _p(d_u),
+                         _p(d_x), _p(dW), _p(db))
+    return dict(d_x=d_x, dconv_w=dW, dconv_b=db)

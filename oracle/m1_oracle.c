@@ -659,3 +659,63 @@ ORC_API int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------------ */
+/* Standalone conv1d + SiLU over a sequence and its backward, for the        */
+/* kernels that run the conv as a separate launch.                           */
+/*   forward : prefill.rs:178-225 (== cpu/forward.rs:157-191)                */
+/*   backward: cpu/backward.rs:228-274 + backward_ops.rs:22-58               */
+/* conv_state [B,D,K] is the GPU-convention window, in/out for the forward,  */
+/* the ENTERING window for the backward.  dW/db accumulate (+=).             */
+/* ------------------------------------------------------------------------ */
+ORC_API int orc_conv1d_fwd(int B, int T, int D, int K, const float *x, long ld_x,
+                           const float *w, const float *bias, float *conv_state, float *u) {
+    for (int b = 0; b < B; b++)
+        for (int d = 0; d < D; d++) {
+            float *reg = conv_state + ((size_t)b * D + d) * K;
+            for (int t = 0; t < T; t++) {
+                for (int k = 0; k < K - 1; k++) reg[k] = reg[k + 1];
+                reg[K - 1] = x[((size_t)b * T + t) * ld_x + d];
+                float val = bias[d];
+                for (int k = 0; k < K; k++) val += reg[k] * w[(size_t)d * K + k];
+                u[((size_t)b * T + t) * D + d] = silu_div(val);
+            }
+        }
+    return 0;
+}
+
+ORC_API int orc_conv1d_bwd(int B, int T, int D, int K, const float *x, long ld_x,
+                           const float *w, const float *bias, const float *conv_state0,
+                           const float *d_u, float *d_x, float *dW, float *db) {
+    float *carry = (float *)malloc(sizeof(float) * (size_t)D * (K > 1 ? K - 1 : 1));
+    float *win = (float *)malloc(sizeof(float) * (size_t)K);
+    for (int b = 0; b < B; b++) {
+        memset(carry, 0, sizeof(float) * (size_t)D * (K > 1 ? K - 1 : 1));
+        for (int t = T - 1; t >= 0; t--)
+            for (int d = 0; d < D; d++) {
+                for (int k = 0; k < K; k++) {
+                    long src = (long)t - (K - 1) + k;
+                    if (src >= 0) win[k] = x[((size_t)b * T + src) * ld_x + d];
+                    else win[k] = conv_state0 ? conv_state0[((size_t)b * D + d) * K + K + src] : 0.0f;
+                }
+                float p = bias[d];
+                for (int k = 0; k < K; k++) p += win[k] * w[(size_t)d * K + k];
+                float sg = 1.0f / (1.0f + orc_fast_exp_scalar(-p));
+                float dco = d_u[((size_t)b * T + t) * D + d] * sg * (1.0f + p * (1.0f - sg));
+                db[d] += dco;
+                for (int k = 0; k < K; k++) dW[(size_t)d * K + k] += dco * win[k];
+                float dx = dco * w[(size_t)d * K + K - 1];
+                if (K > 1) {
+                    int cst = K - 1;
+                    float *c = carry + (size_t)d * cst;
+                    dx += c[0];
+                    for (int k = 0; k + 1 < cst; k++) c[k] = c[k + 1] + dco * w[(size_t)d * K + K - 2 - k];
+                    c[cst - 1] = dco * w[(size_t)d * K];
+                }
+                d_x[((size_t)b * T + t) * D + d] = dx;
+            }
+    }
+    free(carry);
+    free(win);
+    return 0;
+}
