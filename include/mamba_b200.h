@@ -243,6 +243,34 @@ MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream, const mamba
 MAMBA_B200_API long long mamba_b200_conv1d_bwd_workspace_bytes(int B, int T, int D, int K);
 MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream, const mamba_b200_conv1d_args* args);
 
+/*
+ * conv1d backward for callers that cannot allocate: identical to
+ * mamba_b200_conv1d_bwd, except that the partial-sum scratch is a fixed 16 MiB
+ * array inside the library (workspace / workspace_bytes in `args` are ignored).
+ * This entry point has no counterpart in the reference.
+ *
+ * It is meant for an engine that must not create device memory on this path:
+ * one that handed its whole budget to an arena sized before this kernel's
+ * scratch was known, or one that runs beside latency-critical streams, which a
+ * cudaMalloc would stall because it synchronises the device (and which can
+ * simply fail when another allocator owns the remaining memory).  The call
+ * makes no cudaMalloc / cudaFree and calls no allocating library routine.
+ *
+ *   - Limit: B * ceil(T/64) * D * (K+1) * 4 bytes must not exceed
+ *     mamba_b200_conv1d_bwd_static_max_bytes() (16 MiB); larger problems are
+ *     refused with MAMBA_B200_ERR_SHAPE and a message, nothing is launched.
+ *   - Every GPU that loads the library holds the 16 MiB until the process exits.
+ *   - The first call on a device looks up the array's device address (with the
+ *     caller's current device, which must be the one `stream` belongs to); make
+ *     that first call before starting any stream capture.
+ *   - All calls on a device share the array: two calls whose kernels can overlap
+ *     on the GPU (different streams, no ordering) race.  Nothing needs clearing
+ *     between calls; each call overwrites every partial it later reads.
+ *   - `handle` may be NULL (failures are then reported by return code alone).
+ */
+MAMBA_B200_API long long mamba_b200_conv1d_bwd_static_max_bytes(void);
+MAMBA_B200_API int mamba_b200_conv1d_bwd_static(void* handle, void* stream, const mamba_b200_conv1d_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -362,3 +362,61 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;
 }
+
+// ---------------------------------------------------------------------------
+// conv1d backward with built-in scratch: an entry point that allocates nothing.
+// ---------------------------------------------------------------------------
+namespace mb200 {
+
+// 16 MiB of partial-sum scratch that lives in the library image.  Every GPU
+// that loads the library carries it until the process exits.
+constexpr long long kStaticScratchFloats = 4ll * 1024 * 1024;
+static __device__ __align__(256) float g_conv_bwd_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+// Device address of g_conv_bwd_scratch per device ordinal.  In host code the
+// symbol itself is only a stand-in; the address a kernel may dereference comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static float* g_scratch_addr[kMaxDevices] = {nullptr};
+
+static int static_scratch_for_current_device(float** out, int* device) {
+    if (cudaGetDevice(device) != cudaSuccess) return MAMBA_B200_ERR_CUDA;
+    if (*device < 0 || *device >= kMaxDevices) return MAMBA_B200_ERR_DEVICE;
+    if (!g_scratch_addr[*device]) {
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_conv_bwd_scratch) != cudaSuccess || !ptr)
+            return MAMBA_B200_ERR_CUDA;
+        g_scratch_addr[*device] = ptr;
+    }
+    *out = g_scratch_addr[*device];
+    return MAMBA_B200_OK;
+}
+
+}  // namespace mb200
+
+extern "C" MAMBA_B200_API long long mamba_b200_conv1d_bwd_static_max_bytes(void) {
+    return kStaticScratchFloats * static_cast<long long>(sizeof(float));
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd_static(void* handle, void* stream,
+                                                           const mamba_b200_conv1d_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);  // may be null: then failures are reported by code only
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "conv1d_bwd_static: null args");
+    mamba_b200_conv1d_args a = *ap;
+    const long long need = mamba_b200_conv1d_bwd_workspace_bytes(a.B, a.T, a.D, a.K);
+    if (need > mamba_b200_conv1d_bwd_static_max_bytes())
+        return fail(c, MAMBA_B200_ERR_SHAPE,
+                    "conv1d_bwd_static: B=%d T=%d D=%d K=%d needs %lld bytes of scratch, the built-in "
+                    "array holds %lld; use mamba_b200_conv1d_bwd with a caller workspace",
+                    a.B, a.T, a.D, a.K, need, mamba_b200_conv1d_bwd_static_max_bytes());
+    float* scratch = nullptr;
+    int device = -1;
+    int rc = static_scratch_for_current_device(&scratch, &device);
+    if (rc) return fail(c, rc, "conv1d_bwd_static: cannot resolve the scratch address on device %d", device);
+    a.workspace = scratch;
+    a.workspace_bytes = mamba_b200_conv1d_bwd_static_max_bytes();
+    // Every partial the reduction reads is written by this call's first kernel,
+    // so nothing left over from an earlier call needs clearing.
+    Ctx local;
+    return mamba_b200_conv1d_bwd(c ? c : &local, stream, &a);
+}
