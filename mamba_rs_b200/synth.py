@@ -66,3 +66,29 @@ def m1_fwd_algorithmic_bytes(B, T, D, N, esize, K=0, z=True):
     if K:
         total += 2 * 4 * B * D * K + 4 * D * (K + 1)
     return total
+
+
+def m3_ssd_inputs(B, T, nh, hd, N, seed=0):
+    """Inputs of the Mamba-3 SISO SSD op (float32): x, K, Q ~ N(0,1) (K and Q
+    scaled by N^-1/4 each so q.k stays O(1)); per-head A = -exp(U[ln 1, ln 16]);
+    dt = softplus(0.5*N(0,1) + dt_bias), dt_bias as for Mamba-1; trap =
+    sigmoid(N(0,1)); adt = A*dt; D = 1."""
+    rng = np.random.default_rng(seed)
+    f = np.float32
+    x = rng.standard_normal((B, T, nh * hd), dtype=f)
+    sc = f(N) ** f(-0.25)
+    K = rng.standard_normal((B, T, nh, N), dtype=f) * sc
+    Q = rng.standard_normal((B, T, nh, N), dtype=f) * sc
+    A = -np.exp(rng.uniform(np.log(1.0), np.log(16.0), size=nh)).astype(f)
+    dt_bias = inv_softplus(np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=nh))).astype(f)
+    raw = 0.5 * rng.standard_normal((B, T, nh), dtype=f) + dt_bias
+    dt = np.log1p(np.exp(raw.astype(np.float64))).astype(f)
+    trap = (1.0 / (1.0 + np.exp(-rng.standard_normal((B, T, nh))))).astype(f)
+    adt = (A[None, None, :] * dt).astype(f)
+    return dict(x=x, K=K, Q=Q, dt=dt, trap=trap, adt=adt, Dh=np.ones(nh, f), A=A)
+
+
+def m3_fwd_algorithmic_bytes(B, T, nh, hd, N, esize):
+    """x and y, K and Q once each, dt/trap/adt f32, final state out."""
+    return (2 * esize * B * T * nh * hd + 2 * esize * B * T * nh * N + 3 * 4 * B * T * nh
+            + 4 * B * nh * hd * N)

@@ -302,3 +302,65 @@ def conv1d_bwd(x, w, bias, d_u, conv_state0=None):
     lib().orc_conv1d_bwd(B, T, D, K, _p(x), C.c_long(D), _p(w), _p(bias), _p(conv_state0), _p(d_u),
                          _p(d_x), _p(dW), _p(db))
     return dict(d_x=d_x, dconv_w=dW, dconv_b=db)
+
+
+# -- Mamba-3 SISO SSD ---------------------------------------------------------
+
+class M3Shape(C.Structure):
+    _fields_ = [("B", C.c_int), ("T", C.c_int), ("nh", C.c_int), ("hd", C.c_int), ("N", C.c_int)]
+
+
+def m3_ssd_fwd(x, K, Q, dt, trap, adt, Dh, ssm=None, kst=None, vst=None, want_h=False):
+    """Sequential definition.  x [B,T,nh*hd]; K,Q [B,T,nh,N]; dt,trap,adt [B,T,nh];
+    Dh [nh].  Returns dict(y, ssm_state [B,nh,hd,N], k_state, v_state, h_all)."""
+    x, K, Q, dt, trap, adt, Dh = map(_f32, (x, K, Q, dt, trap, adt, Dh))
+    B, T, nh, N = K.shape
+    hd = x.shape[2] // nh
+    s = M3Shape(B, T, nh, hd, N)
+    ssm = np.zeros((B, nh, hd, N), np.float32) if ssm is None else _f32(ssm).copy()
+    kst = np.zeros((B, nh, N), np.float32) if kst is None else _f32(kst).copy()
+    vst = np.zeros((B, nh, hd), np.float32) if vst is None else _f32(vst).copy()
+    y = np.empty((B, T, nh * hd), np.float32)
+    h_all = np.empty((B, T + 1, nh, hd, N), np.float32) if want_h else None
+    lib().orc_m3_ssd_fwd(C.byref(s), _p(x), _p(K), _p(Q), _p(dt), _p(trap), _p(adt), _p(Dh), _p(ssm),
+                         _p(kst), _p(vst), _p(y), _p(h_all))
+    return dict(y=y, ssm_state=ssm, k_state=kst, v_state=vst, h_all=h_all)
+
+
+def m3_ssd_fwd_f64(x, K, Q, dt, trap, adt, Dh):
+    f = lambda a: np.ascontiguousarray(a, dtype=np.float64)
+    x, K, Q, dt, trap, adt, Dh = map(f, (x, K, Q, dt, trap, adt, Dh))
+    B, T, nh, N = K.shape
+    s = M3Shape(B, T, nh, x.shape[2] // nh, N)
+    y = np.empty((B, T, x.shape[2]))
+    d = np.float64
+    lib().orc_m3_ssd_fwd_f64(C.byref(s), _p(x, d), _p(K, d), _p(Q, d), _p(dt, d), _p(trap, d), _p(adt, d),
+                             _p(Dh, d), _p(y, d))
+    return y
+
+
+def m3_ssd_fwd_chunked(x, K, Q, dt, trap, adt, Dh, chunk=64):
+    x, K, Q, dt, trap, adt, Dh = map(_f32, (x, K, Q, dt, trap, adt, Dh))
+    B, T, nh, N = K.shape
+    hd = x.shape[2] // nh
+    s = M3Shape(B, T, nh, hd, N)
+    y = np.empty((B, T, nh * hd), np.float32)
+    fs = np.empty((B, nh, hd, N), np.float32)
+    lib().orc_m3_ssd_fwd_chunked(C.byref(s), C.c_int(chunk), _p(x), _p(K), _p(Q), _p(dt), _p(trap),
+                                 _p(adt), _p(Dh), _p(y), _p(fs))
+    return dict(y=y, ssm_state=fs)
+
+
+def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy):
+    x, K, Q, dt, trap, adt, Dh, dy = map(_f32, (x, K, Q, dt, trap, adt, Dh, dy))
+    B, T, nh, N = K.shape
+    hd = x.shape[2] // nh
+    s = M3Shape(B, T, nh, hd, N)
+    z = lambda *sh: np.zeros(sh, np.float32)
+    out = dict(dx=z(B, T, nh * hd), dK=z(B, T, nh, N), dQ=z(B, T, nh, N), d_alpha=z(B, T, nh),
+               d_beta=z(B, T, nh), d_gamma=z(B, T, nh), d_adt=z(B, T, nh), d_dt=z(B, T, nh),
+               d_trap=z(B, T, nh), dD=z(nh))
+    lib().orc_m3_ssd_bwd(C.byref(s), _p(x), _p(K), _p(Q), _p(dt), _p(trap), _p(adt), _p(Dh), _p(dy),
+                         *[_p(out[k]) for k in ("dx", "dK", "dQ", "d_alpha", "d_beta", "d_gamma", "d_adt",
+                                                "d_dt", "d_trap", "dD")])
+    return out
