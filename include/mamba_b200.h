@@ -244,6 +244,43 @@ MAMBA_B200_API long long mamba_b200_conv1d_bwd_workspace_bytes(int B, int T, int
 MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream, const mamba_b200_conv1d_args* args);
 
 /*
+ * Mamba-3 SISO SSD scan (trapezoidal recurrence), forward.  Inputs are exactly
+ * what the reference's chunked kernels consume: one call replaces
+ * m3_preprocess_chunks, m3_dA_cumsum, m3_chunk_state_fwd, m3_state_passing_fwd,
+ * m3_chunk_scan_fwd and m3_writeback_parallel_states
+ * (kernels/mamba3_chunked.cu:57-419, :1050-1242; src/mamba3_siso/gpu/forward.rs:258-421),
+ * and, with carry_in = 1, m3_burnin_fwd[_nosave] (kernels/mamba3_ssd.cu:229-546).
+ *   x [B,T,nh*hd], K, Q [B,T,nh,N] (after bias + RoPE), y [B,T,nh*hd]: storage dtype
+ *   dt (after softplus), trap (after sigmoid), adt = A*dt: [B,T,nh] f32; Dh [nh] f32
+ *   ssm_state [B,nh,hd,N], k_state [B,nh,N], v_state [B,nh,hd] f32: written with
+ *   the state after the window (NULL = not written); read first when carry_in = 1.
+ * 16-bit storage with hd = 64, N = 128 and no carried state runs the chunked
+ * form on tcgen05 tensor cores with the running state in TMEM (no chunk-state or
+ * K_scaled tensors in HBM); every other case runs the sequential definition.
+ * hd and N are not limited to the reference's hd <= 32, N <= 64
+ * (src/mamba3_siso/config.rs:66-99); N <= 128.
+ */
+typedef struct mamba_b200_m3_ssd_args {
+    int dtype;
+    int B, T, nh, hd, N;
+    const void* x;
+    const void* K;
+    const void* Q;
+    const float* dt;
+    const float* trap;
+    const float* adt;
+    const float* Dh;
+    void* y;
+    float* ssm_state;
+    float* k_state;
+    float* v_state;
+    int carry_in;         /* 1: continue from the given state (sequential kernel) */
+    int force_sequential; /* 1: never take the tensor-core path (for comparison) */
+} mamba_b200_m3_ssd_args;
+
+MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream, const mamba_b200_m3_ssd_args* args);
+
+/*
  * conv1d backward for callers that cannot allocate: identical to
  * mamba_b200_conv1d_bwd, except that the partial-sum scratch is a fixed 16 MiB
  * array inside the library (workspace / workspace_bytes in `args` are ignored).

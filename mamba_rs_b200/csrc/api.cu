@@ -41,6 +41,7 @@ bool make_tmap_3d(Ctx* c, CUtensorMap* map, int dtype, const void* base, long lo
 
 int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limits
 int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
+int m3_configure(Ctx* c);       // m3_ssd.cu
 
 }  // namespace mb200
 
@@ -72,6 +73,8 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     int rc = m1_fwd_configure(c);
     if (rc) return rc;
     rc = m1_bwd_configure(c);
+    if (rc) return rc;
+    rc = m3_configure(c);
     if (rc) return rc;
     return MAMBA_B200_OK;
 }

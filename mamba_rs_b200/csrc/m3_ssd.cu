@@ -1,0 +1,514 @@
+// Mamba-3 SISO SSD scan (trapezoidal recurrence) forward for sm_100a.
+//
+// Two kernels behind one entry point:
+//  * m3_ssd_fwd_tc_kernel — chunked form on the 5th-generation tensor cores
+//    (tcgen05.mma, accumulators in TMEM) for 16-bit storage, headdim 64,
+//    d_state 128: per (sample, head) one CTA walks 128-step chunks and keeps
+//    the running state S^T [N x hd] f32 resident in TMEM, so the entering states
+//    never touch HBM (the reference writes [B, chunks, nh, hd, N] f32 of them).
+//    Per chunk: G = Q K^T, decay/causal mask in registers, Y1 = M V,
+//    Y2 = Q S_in^T, S^T <- exp(dA_end) S^T + K^T (w o V).
+//  * m3_ssd_seq_kernel — the sequential definition (one thread per
+//    (sample, head, p), state in registers) for every other shape / dtype and
+//    whenever a recurrent state is carried in.
+#include <string.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace mb200 {
+
+struct M3Params {
+    const void *x, *K, *Q;
+    const float *dt, *trap, *adt, *Dh;
+    void* y;
+    float *ssm_state, *k_state, *v_state;  // in/out (may be null: zero in, not written)
+    int B, T, nh, hd, N;
+    int carry_in;  // 1: the state buffers hold a state to continue from
+    int* status;
+};
+
+// ---------------------------------------------------------------------------
+// Sequential definition, src/mamba3_siso/cpu/forward.rs:85-138 / kernels/mamba3_ssd.cu:229-348:
+//   h = alpha h + (beta v_prev) k_prev + (gamma x) k ;  y = <h, q> + D x
+// grid (nh, B), block hd threads (rounded up to a warp); k, q, k_prev staged in
+// shared memory per step.
+// ---------------------------------------------------------------------------
+template <typename Tact, int NMAX>
+__global__ void m3_ssd_seq_kernel(const M3Params p) {
+    extern __shared__ float sm[];
+    float* ks = sm;                // [2][N] current / previous k
+    float* qs = sm + 2 * p.N;      // [N]
+    const int h = blockIdx.x, b = blockIdx.y, pp = threadIdx.x;
+    const int N = p.N, hd = p.hd, nh = p.nh, T = p.T;
+    const bool act = pp < hd;
+    float st[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) st[n] = 0.0f;
+    float vprev = 0.0f;
+    if (p.carry_in) {
+        if (act) {
+#pragma unroll
+            for (int n = 0; n < NMAX; ++n)
+                if (n < N) st[n] = p.ssm_state[((static_cast<long long>(b) * nh + h) * hd + pp) * N + n];
+            vprev = p.v_state[(static_cast<long long>(b) * nh + h) * hd + pp];
+        }
+        for (int n = threadIdx.x; n < N; n += blockDim.x)
+            ks[N + n] = p.k_state[(static_cast<long long>(b) * nh + h) * N + n];
+    } else {
+        for (int n = threadIdx.x; n < N; n += blockDim.x) ks[N + n] = 0.0f;
+    }
+    const Tact* xb = static_cast<const Tact*>(p.x);
+    const Tact* Kb = static_cast<const Tact*>(p.K);
+    const Tact* Qb = static_cast<const Tact*>(p.Q);
+    Tact* yb = static_cast<Tact*>(p.y);
+    const float Dv = p.Dh[h];
+    for (int t = 0; t < T; ++t) {
+        const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+        const int cur = t & 1, prv = cur ^ 1;  // ks[cur] <- k_t ; ks[prv] holds k_{t-1}
+        __syncthreads();
+        for (int n = threadIdx.x; n < N; n += blockDim.x) {
+            ks[cur * N + n] = to_f(Kb[th * N + n]);
+            qs[n] = to_f(Qb[th * N + n]);
+        }
+        __syncthreads();
+        const float alpha = ex2(p.adt[th] * kLog2e);
+        const float beta = alpha * p.dt[th] * (1.0f - p.trap[th]);
+        const float gamma = p.trap[th] * p.dt[th];
+        if (act) {
+            const float xv = to_f(xb[(static_cast<long long>(b) * T + t) * nh * hd + h * hd + pp]);
+            const float bv = beta * vprev, gx = gamma * xv;
+            float acc = 0.0f;
+            const float* kc = ks + cur * N;
+            const float* kp = ks + prv * N;
+#pragma unroll
+            for (int n = 0; n < NMAX; ++n)
+                if (n < N) {
+                    st[n] = fmaf(alpha, st[n], fmaf(bv, kp[n], gx * kc[n]));
+                    acc = fmaf(st[n], qs[n], acc);
+                }
+            yb[(static_cast<long long>(b) * T + t) * nh * hd + h * hd + pp] = from_f<Tact>(fmaf(Dv, xv, acc));
+            vprev = xv;
+        }
+    }
+    // T == 0 leaves the state untouched; otherwise ks[(T-1)&1] holds the last k.
+    if (T > 0) {
+        if (p.ssm_state && act) {
+#pragma unroll
+            for (int n = 0; n < NMAX; ++n)
+                if (n < N) p.ssm_state[((static_cast<long long>(b) * nh + h) * hd + pp) * N + n] = st[n];
+        }
+        if (p.v_state && act) p.v_state[(static_cast<long long>(b) * nh + h) * hd + pp] = vprev;
+        __syncthreads();
+        if (p.k_state)
+            for (int n = threadIdx.x; n < N; n += blockDim.x)
+                p.k_state[(static_cast<long long>(b) * nh + h) * N + n] = ks[((T - 1) & 1) * N + n];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// tcgen05 / TMEM chunked kernel.  hd = 64, N = 128, chunk = 128, 128 threads.
+// ---------------------------------------------------------------------------
+namespace tc {
+
+constexpr int CS = 128, HD = 64, NS = 128;
+// Shared-memory operand tiles: 8-row x 16-byte core matrices (no swizzle).  A
+// tile of R rows x C 16-bit columns keeps core (r/8, c/8) at
+// (r/8)*(C/8)*128 + (c/8)*128 bytes, row r%8 at +16*(r%8).
+constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kVw = 81920, kM = 98304, kS = 131072;
+constexpr uint32_t kVec = 147456;  // f32 dA[128], scale[128], gamma[128]
+constexpr uint32_t kBar = kVec + 3 * 128 * 4, kTmemSlot = kBar + 16;
+constexpr uint32_t kSmem = kTmemSlot + 16;
+// TMEM columns of the four f32 accumulators.
+constexpr uint32_t cG = 0, cY1 = 128, cY2 = 192, cS = 256, kTmemCols = 512;
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // start >> 4 [0,14) | LBO >> 4 [16,30) | SBO >> 4 [32,46) | version 1 [46,48) | no swizzle
+    return static_cast<uint64_t>((addr & 0x3FFFF) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46);
+}
+// kind::f16 instruction descriptor: f32 accumulate, 16-bit A/B of format `fmt`
+// (0 = f16, 1 = bf16), majors (0 = K-major, 1 = MN-major), M = 128.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t fmt, uint32_t a_mn, uint32_t b_mn, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) |
+           ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate ? 1u : 0u)
+        : "memory");
+}
+__device__ __forceinline__ void commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive f32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
+        "%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <typename Th> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename Th> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+
+// Byte offset of the 16-byte chunk (row r, 8-column group j) in a tile of C columns.
+__device__ __forceinline__ uint32_t chunk_off(int r, int j, int C) {
+    return static_cast<uint32_t>((r >> 3) * (C >> 3) * 128 + j * 128 + (r & 7) * 16);
+}
+
+template <typename Th>
+__global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int T = p.T, nh = p.nh;
+    constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
+    float* dA = reinterpret_cast<float*>(smem + kVec);
+    float* scl = dA + 128;
+    float* gam = dA + 256;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
+    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
+    const uint32_t sbase = smem_u32(smem);
+
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tslot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tslot;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);  // this warp's 32 lanes
+
+    const Th* xg = static_cast<const Th*>(p.x);
+    const Th* Kg = static_cast<const Th*>(p.K);
+    const Th* Qg = static_cast<const Th*>(p.Q);
+    Th* yg = static_cast<Th*>(p.y);
+    const float Dv = p.Dh[h];
+    const int nchunks = (T + CS - 1) / CS;
+    bool ok = true;
+
+    for (int c = 0; c < nchunks; ++c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const int t = t0 + tid;  // this thread's row
+        const bool row_ok = tid < nv;
+        // ---- 1. load row `tid` of Q, K, V into the core-matrix tiles; per-row scalars ----
+        {
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
+            const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+#pragma unroll
+            for (int j = 0; j < NS / 8; ++j) {
+                uint4 q = zero, k = zero;
+                if (row_ok) {
+                    q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
+                    k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
+                }
+                *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = q;
+                *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
+            }
+            float a = 0.0f, g = 0.0f, s = 0.0f;
+            if (row_ok) {
+                const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+                a = p.adt[th];
+                g = p.dt[th] * p.trap[th];
+                s = g;
+                if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
+            }
+            // inclusive cumsum of adt over the chunk: warp scan + warp totals
+            float run = a;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const float o = __shfl_up_sync(0xffffffffu, run, m);
+                if ((tid & 31) >= m) run += o;
+            }
+            if ((tid & 31) == 31) dA[warp] = run;  // slot reused below after the barrier
+            gam[tid] = g;
+            scl[tid] = s;
+            __syncthreads();
+            float off = 0.0f;
+            for (int w = 0; w < warp; ++w) off += dA[w];
+            __syncthreads();
+            run += off;
+            dA[tid] = run;
+            __syncthreads();
+            const float dA_end = dA[nv - 1];
+            const float wt = row_ok ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                uint4 v = zero;
+                if (row_ok) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
+                *reinterpret_cast<uint4*>(smem + kV + chunk_off(tid, j, HD)) = v;
+                uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float2 f = unpack2<Th>(w4[q4]);
+                    w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
+                }
+                *reinterpret_cast<uint4*>(smem + kVw + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+        }
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        // ---- 2. G = Q K^T (and Y2 = Q S_in^T for c > 0) ----
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idG = instr_desc(fmt, 0, 0, 128), idY = instr_desc(fmt, 0, 1, 64);
+#pragma unroll
+            for (int k = 0; k < NS / 16; ++k) {
+                const uint64_t a = smem_desc(sbase + kQ + k * 256, 128, 2048);
+                const uint64_t bb = smem_desc(sbase + kK + k * 256, 128, 2048);
+                mma(tmem + cG, a, bb, idG, k > 0);
+            }
+            if (c > 0) {
+#pragma unroll
+                for (int k = 0; k < NS / 16; ++k) {
+                    const uint64_t a = smem_desc(sbase + kQ + k * 256, 128, 2048);
+                    const uint64_t bb = smem_desc(sbase + kS + k * 2048, 1024, 128);  // N = p, K = n
+                    mma(tmem + cY2, a, bb, idY, k > 0);
+                }
+            }
+            commit(&bars[0]);
+        }
+        ok = mbar_wait(&bars[0], c & 1, p.status) && ok;
+        fence_after();
+        // ---- 3. decay / causal mask -> M (A operand of M V); rescale the running state ----
+        {
+            const float dAt = dA[tid], gt = gam[tid];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                float g[32];
+                tmem_ld32(lane_addr + cG + q4 * 32, g);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float m2[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int s = q4 * 32 + i + u;
+                        float m = 0.0f;
+                        if (s < tid) m = g[i + u] * scl[s] * ex2((dAt - dA[s]) * kLog2e);
+                        else if (s == tid) m = fmaf(g[i + u], gt, Dv);
+                        m2[u] = (row_ok && s < nv) ? m : 0.0f;
+                    }
+                    packed[i / 2] = pack2<Th>(m2[0], m2[1]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) =
+                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            }
+            if (c > 0) {  // S^T row `tid` (state index n = tid) *= exp(dA_end)
+                const float e_end = ex2(dA[nv - 1] * kLog2e);
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2) {
+                    float sv[32];
+                    tmem_ld32(lane_addr + cS + q2 * 32, sv);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sv[i] *= e_end;
+                    tmem_st32(lane_addr + cS + q2 * 32, sv);
+                }
+            }
+        }
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        // ---- 4. Y1 = M V ;  S^T += K^T (w o V) ----
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idY = instr_desc(fmt, 0, 1, 64), idS = instr_desc(fmt, 1, 1, 64);
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k) {
+                const uint64_t a = smem_desc(sbase + kM + k * 256, 128, 2048);
+                const uint64_t bb = smem_desc(sbase + kV + k * 2048, 1024, 128);  // N = p, K = s
+                mma(tmem + cY1, a, bb, idY, k > 0);
+            }
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k) {
+                const uint64_t a = smem_desc(sbase + kK + k * 4096, 2048, 128);   // M = n, K = t
+                const uint64_t bb = smem_desc(sbase + kVw + k * 2048, 1024, 128);  // N = p, K = t
+                mma(tmem + cS, a, bb, idS, c > 0 || k > 0);
+            }
+            commit(&bars[1]);
+        }
+        ok = mbar_wait(&bars[1], c & 1, p.status) && ok;
+        fence_after();
+        // ---- 5. epilogue: y row; 16-bit copy of the new state for the next chunk ----
+        {
+            const float e_t = ex2(dA[tid] * kLog2e);
+            const long long y_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                float y1[32], y2[32];
+                tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
+                if (c > 0) {
+                    tmem_ld32(lane_addr + cY2 + q2 * 32, y2);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) y1[i] = fmaf(e_t, y2[i], y1[i]);
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
+                            make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
+                                       pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
+                }
+                float sv[32];
+                tmem_ld32(lane_addr + cS + q2 * 32, sv);
+                if (c + 1 < nchunks) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(smem + kS + chunk_off(tid, q2 * 4 + j, HD)) =
+                            make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
+                                       pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
+                } else if (p.ssm_state) {  // final state [b, h, p, n], n = tid
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        p.ssm_state[((static_cast<long long>(b) * nh + h) * HD + q2 * 32 + i) * NS + tid] = sv[i];
+                }
+            }
+        }
+        fence_before();
+        __syncthreads();
+        fence_after();
+    }
+    // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
+    if (T > 0) {
+        const long long last = static_cast<long long>(b) * T + (T - 1);
+        if (p.k_state) p.k_state[(static_cast<long long>(b) * nh + h) * NS + tid] = to_f(Kg[(last * nh + h) * NS + tid]);
+        if (p.v_state && tid < HD)
+            p.v_state[(static_cast<long long>(b) * nh + h) * HD + tid] = to_f(xg[last * nh * HD + h * HD + tid]);
+    }
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    (void)ok;
+}
+
+}  // namespace tc
+
+int m3_configure(Ctx* c) {
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__half>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem));
+    return MAMBA_B200_OK;
+}
+
+template <typename Tact>
+static void launch_seq(const M3Params& p, cudaStream_t st) {
+    dim3 grid(p.nh, p.B);
+    const int threads = ((p.hd + 31) / 32) * 32;
+    const size_t smem = sizeof(float) * 3 * p.N;
+    if (p.N <= 16) m3_ssd_seq_kernel<Tact, 16><<<grid, threads, smem, st>>>(p);
+    else if (p.N <= 32) m3_ssd_seq_kernel<Tact, 32><<<grid, threads, smem, st>>>(p);
+    else if (p.N <= 64) m3_ssd_seq_kernel<Tact, 64><<<grid, threads, smem, st>>>(p);
+    else m3_ssd_seq_kernel<Tact, 128><<<grid, threads, smem, st>>>(p);
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
+                                                    const mamba_b200_m3_ssd_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: null args");
+    const mamba_b200_m3_ssd_args& a = *ap;
+    if (!dtype_ok(a.dtype)) return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: bad dtype %d", a.dtype);
+    if (a.B < 0 || a.T < 0 || a.nh <= 0 || a.hd <= 0 || a.N <= 0)
+        return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: bad dims");
+    if (a.hd > 1024 || a.N > 128)
+        return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: headdim %d > 1024 or d_state %d > 128", a.hd, a.N);
+    if (a.B == 0 || a.T == 0) return MAMBA_B200_OK;
+    if (a.B > 65535) return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: batch %d > 65535", a.B);
+    if (!a.x || !a.K || !a.Q || !a.dt || !a.trap || !a.adt || !a.Dh || !a.y)
+        return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: null required pointer");
+    if (a.carry_in && (!a.ssm_state || !a.k_state || !a.v_state))
+        return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: carry_in needs all three state buffers");
+    M3Params p;
+    memset(&p, 0, sizeof(p));
+    p.x = a.x; p.K = a.K; p.Q = a.Q; p.dt = a.dt; p.trap = a.trap; p.adt = a.adt; p.Dh = a.Dh; p.y = a.y;
+    p.ssm_state = a.ssm_state; p.k_state = a.k_state; p.v_state = a.v_state;
+    p.B = a.B; p.T = a.T; p.nh = a.nh; p.hd = a.hd; p.N = a.N; p.carry_in = a.carry_in;
+    p.status = c->d_status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd == tc::HD && a.N == tc::NS && !a.carry_in &&
+                             !a.force_sequential && al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.y);
+    if (tensor_core) {
+        dim3 grid(a.nh, a.B);
+        if (a.dtype == MAMBA_B200_BF16)
+            tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16><<<grid, 128, tc::kSmem, st>>>(p);
+        else
+            tc::m3_ssd_fwd_tc_kernel<__half><<<grid, 128, tc::kSmem, st>>>(p);
+    } else {
+        if (a.dtype == MAMBA_B200_F32) launch_seq<float>(p, st);
+        else if (a.dtype == MAMBA_B200_F16) launch_seq<__half>(p, st);
+        else launch_seq<__nv_bfloat16>(p, st);
+    }
+    MB200_CUDA_CHECK(c, cudaGetLastError());
+    return MAMBA_B200_OK;
+}

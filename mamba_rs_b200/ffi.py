@@ -82,6 +82,17 @@ class Conv1dArgs(C.Structure):
     ]
 
 
+class M3SsdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("T", C.c_int), ("nh", C.c_int), ("hd", C.c_int), ("N", C.c_int),
+        ("x", C.c_void_p), ("K", C.c_void_p), ("Q", C.c_void_p),
+        ("dt", C.c_void_p), ("trap", C.c_void_p), ("adt", C.c_void_p), ("Dh", C.c_void_p),
+        ("y", C.c_void_p),
+        ("ssm_state", C.c_void_p), ("k_state", C.c_void_p), ("v_state", C.c_void_p),
+        ("carry_in", C.c_int), ("force_sequential", C.c_int),
+    ]
+
+
 _lib = None
 
 
@@ -101,6 +112,7 @@ def lib() -> C.CDLL:
         _lib.mamba_b200_check_status.argtypes = [C.c_void_p, C.c_void_p]
         _lib.mamba_b200_sscan_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanFwdArgs)]
         _lib.mamba_b200_sscan_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanBwdArgs)]
+        _lib.mamba_b200_m3_ssd_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(M3SsdArgs)]
         _lib.mamba_b200_sscan_step.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanStepArgs)]
         _lib.mamba_b200_conv1d_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]
         _lib.mamba_b200_conv1d_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]

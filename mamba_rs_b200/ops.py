@@ -16,7 +16,7 @@ import torch
 from . import ffi
 
 __all__ = ["selective_scan_fwd", "selective_scan_bwd", "selective_scan_bwd_workspace_bytes",
-           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "dtype_code"]
+           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "dtype_code"]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -250,3 +250,36 @@ def conv1d_bwd(x, conv_w, conv_b, d_u, conv_state0=None, *, dconv_w=None, dconv_
         rc = ffi.lib().mamba_b200_conv1d_bwd(h.ptr, _stream(dev), C.byref(a))
     h.check(rc, "mamba_b200_conv1d_bwd")
     return dict(d_x=d_x, dconv_w=dconv_w, dconv_b=dconv_b)
+
+
+def m3_ssd_fwd(x, K, Q, dt, trap, adt, Dh, *, ssm_state=None, k_state=None, v_state=None,
+               carry_in=False, force_sequential=False, y=None, handle=None):
+    """Mamba-3 SISO SSD forward.  x [B,T,nh*hd], K/Q [B,T,nh,N] in the storage
+    dtype (contiguous); dt, trap, adt [B,T,nh] and Dh [nh] f32.  State tensors
+    (f32) receive the state after the window; with carry_in they are read first."""
+    _require_cuda(x, K, Q, dt, trap, adt, Dh, ssm_state, k_state, v_state, y)
+    Bsz, T, nh, N = K.shape
+    hd = x.shape[2] // nh
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    for t, nm in ((x, "x"), (K, "K"), (Q, "Q")):
+        if not t.is_contiguous() or t.dtype != x.dtype:
+            raise ValueError(f"{nm} must be contiguous and share x's dtype")
+    for t, nm in ((dt, "dt"), (trap, "trap"), (adt, "adt"), (Dh, "Dh"), (ssm_state, "ssm_state"),
+                  (k_state, "k_state"), (v_state, "v_state")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError(f"{nm} must be contiguous float32")
+    if y is None:
+        y = torch.empty_like(x)
+    a = ffi.M3SsdArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.T, a.nh, a.hd, a.N = Bsz, T, nh, hd, N
+    a.x, a.K, a.Q = _ptr(x), _ptr(K), _ptr(Q)
+    a.dt, a.trap, a.adt, a.Dh = _ptr(dt), _ptr(trap), _ptr(adt), _ptr(Dh)
+    a.y = _ptr(y)
+    a.ssm_state, a.k_state, a.v_state = _ptr(ssm_state), _ptr(k_state), _ptr(v_state)
+    a.carry_in, a.force_sequential = int(carry_in), int(force_sequential)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_m3_ssd_fwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_m3_ssd_fwd")
+    return y
