@@ -72,10 +72,12 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     MB200_CUDA_CHECK(c, cudaMemset(c->d_status, 0, sizeof(int)));
     int rc = m1_fwd_configure(c);
     if (rc) return rc;
+#ifndef MB200_FWD_TUNING  // tuning builds link the forward kernels only
     rc = m1_bwd_configure(c);
     if (rc) return rc;
     rc = m3_configure(c);
     if (rc) return rc;
+#endif
     return MAMBA_B200_OK;
 }
 

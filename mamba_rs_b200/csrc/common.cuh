@@ -100,6 +100,54 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(
 #endif
 __device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
 
+// ---- B / C vectors ------------------------------------------------------------
+// NS consecutive B or C values of one timestep, held in registers in their
+// storage dtype and widened to f32 pairs at the point of use.
+template <typename Tact, int NS>
+struct StateVec;
+template <int NS>
+struct StateVec<float, NS> {
+    float4 q[NS / 4];
+    __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+        for (int j = 0; j < NS / 4; ++j) q[j] = *reinterpret_cast<const float4*>(p + 4 * j);
+    }
+    __device__ __forceinline__ float2 pair(int j) const {
+        return (j & 1) ? make_float2(q[j / 2].z, q[j / 2].w) : make_float2(q[j / 2].x, q[j / 2].y);
+    }
+};
+template <typename Th, int NS>
+struct StateVecHalf {
+    uint32_t w[NS / 2];  // two 16-bit elements per word
+    __device__ __forceinline__ void load(const Th* p) {
+        if (NS % 8 == 0) {
+#pragma unroll
+            for (int j = 0; j < NS / 8; ++j) {
+                const uint4 v = *reinterpret_cast<const uint4*>(p + 8 * j);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NS / 4; ++j) {
+                const uint2 v = *reinterpret_cast<const uint2*>(p + 4 * j);
+                w[2 * j] = v.x; w[2 * j + 1] = v.y;
+            }
+        }
+    }
+};
+template <int NS>
+struct StateVec<__nv_bfloat16, NS> : StateVecHalf<__nv_bfloat16, NS> {
+    __device__ __forceinline__ float2 pair(int j) const {
+        return make_float2(__uint_as_float(this->w[j] << 16), __uint_as_float(this->w[j] & 0xffff0000u));
+    }
+};
+template <int NS>
+struct StateVec<__half, NS> : StateVecHalf<__half, NS> {
+    __device__ __forceinline__ float2 pair(int j) const {
+        return __half22float2(*reinterpret_cast<const __half2*>(&this->w[j]));
+    }
+};
+
 // ---- mbarrier + TMA ----------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

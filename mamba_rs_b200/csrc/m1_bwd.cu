@@ -1,7 +1,7 @@
 // Mamba-1 fused selective-scan backward (BPTT) for sm_100a, by recomputation.
 //
 // The training-mode forward saves only the state ENTERING each block of S
-// timesteps (S = save_stride, a multiple of 16, at most 64).  One warp owns
+// timesteps (S = save_stride, 32 or 64).  One warp owns
 // (sample b, 32 channels), one channel per lane with all d_state values in
 // registers, and walks the blocks from last to first:
 //   1. TMA brings the block's u, delta, z, dy, B, C tiles (double-buffered
@@ -58,7 +58,8 @@ struct BwdTraits {
     static constexpr size_t OFF_HBUF = 2 * STAGE;                                        // f32 [16][NS][32]
     static constexpr size_t OFF_HB = OFF_HBUF + sizeof(float) * kBwdSub * NS * 32;        // f32 [4][NS][32]
     static constexpr size_t OFF_OUT = OFF_HB + sizeof(float) * (kBwdSMax / kBwdSub) * NS * 32;  // 3 x Tact [S][32]
-    static constexpr size_t OFF_BAR = OFF_OUT + 3 * ACT;
+    static constexpr size_t OFF_DLS = OFF_OUT + 3 * ACT;                                   // f32 delta [S][32]
+    static constexpr size_t OFF_BAR = OFF_DLS + sizeof(float) * kBwdSMax * 32;
     static constexpr size_t SMEM = OFF_BAR + 128;
 };
 
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
     extern __shared__ __align__(128) unsigned char smem[];
     float* hbuf = reinterpret_cast<float*>(smem + Tr::OFF_HBUF);
     float* hb = reinterpret_cast<float*>(smem + Tr::OFF_HB);
+    float* dls = reinterpret_cast<float*>(smem + Tr::OFF_DLS);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Tr::OFF_BAR);
     const int lane = threadIdx.x;
     const int b = blockIdx.y, tile = blockIdx.x, d0 = tile * DT, d = d0 + lane;
@@ -151,8 +153,8 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
     const float Dd = d_ok ? p.Dp[d] : 0.0f;
 
     // exp2(delta * a2[j]) for all j
-    auto decay = [&](float dlv, float* e) {
-        if (geo) {
+    auto decay_t = [&](auto geo_tag, float dlv, float* e) {
+        if (decltype(geo_tag)::value) {
             const float E = ex2(dlv * a2[0]), R = ex2(dlv * a2_step);
             e[0] = E;
 #pragma unroll
@@ -163,11 +165,32 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
         }
     };
 
+    // B or C of one step as f32: one or two 128-bit loads when the row fills the
+    // lane slice, element loads otherwise.
+    const bool vec_bc = N == NS;
+    auto load_row = [&](const Tact* row, float* out) {
+        if (vec_bc) {
+            StateVec<Tact, NS> v;
+            v.load(row);
+#pragma unroll
+            for (int j = 0; j < NS / 2; ++j) {
+                const float2 f = v.pair(j);
+                out[2 * j] = f.x;
+                out[2 * j + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NS; ++j) out[j] = j < N ? to_f(row[j]) : 0.0f;
+        }
+    };
+
     float dh[NS], accA[NS];
     float accD = 0.0f;
 #pragma unroll
     for (int j = 0; j < NS; ++j) dh[j] = accA[j] = 0.0f;
 
+    auto run_blocks = [&](auto geo_tag) {
+    auto decay = [&](float dlv, float* e) { decay_t(geo_tag, dlv, e); };
     for (int it = 0; it < nblk; ++it) {
         const int k = nblk - 1 - it, s = it & 1, t0 = k * S;
         const int nv = min(S, T - t0);
@@ -191,10 +214,13 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
         const Tact* rb = st_b(s);
         const Tact* rc = st_c(s);
 
-        auto delta_at = [&](int r) {
-            float v = to_f(rd[r * DT]);
-            return kSoftplus ? softplusf_fast(v) : v;
-        };
+        // softplus(delta) of the whole block once (three sweeps read it)
+#pragma unroll 4
+        for (int r = 0; r < nv; ++r) {
+            const float v = to_f(rd[r * DT]);
+            dls[r * 32 + lane] = kSoftplus ? softplusf_fast(v) : v;
+        }
+        auto delta_at = [&](int r) { return dls[r * 32 + lane]; };
 
         // ---- 2. state entering each sub-block ----
         float h[NS];
@@ -214,11 +240,11 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
 #pragma unroll 2
             for (int r = sb * kBwdSub; r < (sb + 1) * kBwdSub; ++r) {
                 const float dlv = delta_at(r), duv = dlv * to_f(ru[r * DT]);
-                float e[NS];
+                float e[NS], Bv[NS];
                 decay(dlv, e);
+                load_row(rb + r * N, Bv);
 #pragma unroll
-                for (int j = 0; j < NS; ++j)
-                    h[j] = fmaf(e[j], h[j], duv * (j < N ? to_f(rb[r * N + j]) : 0.0f));
+                for (int j = 0; j < NS; ++j) h[j] = fmaf(e[j], h[j], duv * Bv[j]);
             }
         }
 
@@ -230,18 +256,19 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
 #pragma unroll 2
             for (int r = r_lo; r < r_hi; ++r) {  // forward: keep h_t
                 const float dlv = delta_at(r), duv = dlv * to_f(ru[r * DT]);
-                float e[NS];
+                float e[NS], Bv[NS];
                 decay(dlv, e);
+                load_row(rb + r * N, Bv);
 #pragma unroll
                 for (int j = 0; j < NS; ++j) {
-                    h[j] = fmaf(e[j], h[j], duv * (j < N ? to_f(rb[r * N + j]) : 0.0f));
+                    h[j] = fmaf(e[j], h[j], duv * Bv[j]);
                     hbuf[((r - r_lo) * NS + j) * 32 + lane] = h[j];
                 }
             }
             for (int r = r_hi - 1; r >= r_lo; --r) {  // reverse: BPTT
                 const float uv = to_f(ru[r * DT]);
                 const float raw = to_f(rd[r * DT]);
-                const float dlv = kSoftplus ? softplusf_fast(raw) : raw;
+                const float dlv = delta_at(r);
                 const float dyv = to_f(rdy[r * DT]);
                 float e[NS], hc[NS], hp[NS], Bv[NS], Cv[NS];
                 decay(dlv, e);
@@ -250,9 +277,9 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
                     hc[j] = hbuf[((r - r_lo) * NS + j) * 32 + lane];
                     hp[j] = r > r_lo ? hbuf[((r - r_lo - 1) * NS + j) * 32 + lane]
                                      : hb[(sb * NS + j) * 32 + lane];
-                    Bv[j] = j < N ? to_f(rb[r * N + j]) : 0.0f;
-                    Cv[j] = j < N ? to_f(rc[r * N + j]) : 0.0f;
                 }
+                load_row(rb + r * N, Bv);
+                load_row(rc + r * N, Cv);
                 // pre-gate output and the gate, kernels/elementwise.cu:191-233
                 float ys = Dd * uv;
 #pragma unroll
@@ -339,6 +366,9 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
         if (kGate && !(sm & kBDz)) plain_store(static_cast<Tact*>(p.dz), p.ld_dz, o_dz);
         __syncwarp();
     }
+    };
+    if (geo) run_blocks(std::true_type{});
+    else run_blocks(std::false_type{});
 
     // per-sample parameter-gradient partials
     if (d_ok) {
@@ -472,8 +502,8 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: null required pointer");
     if (a.z_mode < 0 || a.z_mode > 2 || (a.z_mode && (!a.z || !a.d_z)))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: z_mode %d needs z and d_z", a.z_mode);
-    if (a.save_stride < kBwdSub || a.save_stride > kBwdSMax || a.save_stride % kBwdSub)
-        return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: save_stride %d must be 16, 32, 48 or 64", a.save_stride);
+    if (a.save_stride != 32 && a.save_stride != 64)
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: save_stride %d must be 32 or 64", a.save_stride);
     if (a.ld_u < a.D || a.ld_delta < a.D || a.ld_dy < a.D || a.ld_bc < a.N || a.ld_du < a.D ||
         a.ld_ddelta < a.D || (a.z_mode && (a.ld_z < a.D || a.ld_dz < a.D)))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: a row stride is smaller than its row");

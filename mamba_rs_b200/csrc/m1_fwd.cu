@@ -1,6 +1,8 @@
 // Mamba-1 fused selective-scan forward for sm_100a.
 // Host side of the fused forward: argument validation, TMA descriptors, variant
 // selection and launch.  The kernels live in m1_fwd_kernel.cuh.
+#include <stdlib.h>
+
 #include "m1_fwd_kernel.cuh"
 
 namespace mb200 {
@@ -66,9 +68,8 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     for (int i = 0; i < tab.n[a.dtype]; ++i)
         if (vs[i].ns * vs[i].lpc >= a.N) { v = &vs[i]; break; }
     if (!v) return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_fwd: no variant for d_state %d", a.N);
-    if (a.chunk_states && (a.save_stride <= 0 || a.save_stride % v->tc != 0))
-        return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: save_stride %d is not a multiple of %d",
-                    a.save_stride, v->tc);
+    if (a.chunk_states && (a.save_stride <= 0 || a.save_stride % v->tc != 0 || a.save_stride > 64))
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: save_stride %d must be 32 or 64", a.save_stride);
 
     FwdParams p;
     memset(&p, 0, sizeof(p));
@@ -101,7 +102,26 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     if (!fn || v->smem > 227 * 1024)
         return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_fwd: no kernel for dtype %d flags %d d_state %d",
                     a.dtype, flags, a.N);
-    dim3 grid((a.D + v->dt - 1) / v->dt, a.B);
+    // Time segments: when batch x channel tiles cannot even give every warp
+    // scheduler one warp (small-batch prefill), split the sequence; each extra
+    // segment replays the earlier ones for its entering state (about half the
+    // cost of a full chunk), so at most 3 segments.  Measured on B200: no gain
+    // once the schedulers hold 2-3 warps each (the kernel is then bound by
+    // instruction throughput, and replay only adds instructions).
+    const long long tiles = static_cast<long long>((a.D + v->dt - 1) / v->dt) * a.B;
+    const long long warps = tiles * (v->threads / 32);
+    const int nchunks = (a.T + v->tc - 1) / v->tc;
+    int segs = 1;
+    const char* env = getenv("MAMBA_B200_FWD_SEGMENTS");
+    if (env && atoi(env) > 0) segs = atoi(env);
+    else {
+        const long long want = 4ll * c->sm_count;  // one warp per scheduler at least
+        while (segs < 3 && warps * segs < want && nchunks >= 8 * (segs + 1)) ++segs;
+    }
+    if (segs > nchunks) segs = nchunks > 0 ? nchunks : 1;
+    p.seg_chunks = segs > 1 ? (nchunks + segs - 1) / segs : 0;
+    if (segs > 1) segs = (nchunks + p.seg_chunks - 1) / p.seg_chunks;
+    dim3 grid((a.D + v->dt - 1) / v->dt, a.B, segs);
     fn<<<grid, v->threads, v->smem, stream>>>(p);
     MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;

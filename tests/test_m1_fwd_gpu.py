@@ -212,9 +212,10 @@ def test_argument_errors_are_reported_not_launched(cuda_dev):
     with pytest.raises(RuntimeError, match="d_conv"):
         mb.selective_scan_fwd(x, x, bc, bc, a, Dp, conv_w=torch.zeros(16, 9, device=cuda_dev),
                               conv_b=torch.zeros(16, device=cuda_dev))
-    with pytest.raises(RuntimeError, match="save_stride"):
-        mb.selective_scan_fwd(x, x, bc, bc, a, Dp, chunk_states=torch.zeros(1, 1, 16, 16, device=cuda_dev),
-                              save_stride=10)
+    for bad in (10, 16, 128):
+        with pytest.raises(RuntimeError, match="save_stride"):
+            mb.selective_scan_fwd(x, x, bc, bc, a, Dp, chunk_states=torch.zeros(1, 1, 16, 16, device=cuda_dev),
+                                  save_stride=bad)
     # empty batch / empty sequence: accepted, nothing to do
     e = torch.zeros(0, 8, 16, device=cuda_dev)
     assert mb.selective_scan_fwd(e, e, e, e, a, Dp).shape == (0, 8, 16)
