@@ -281,6 +281,46 @@ typedef struct mamba_b200_m3_ssd_args {
 MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream, const mamba_b200_m3_ssd_args* args);
 
 /*
+ * Mamba-3 SISO SSD scan, backward through a window that started from a zero
+ * state.  One call replaces the scan part of the reference's backward:
+ * m3_extract_da_cs_sum, m3_dqkv (with its dD reduce), and the d(dt), d(trap),
+ * d(adt) terms that m3_ddt_dtrap / m3_final_grads derive from the scan
+ * (kernels/mamba3_chunked.cu:439-1035; src/mamba3_siso/gpu/backward.rs:235-457);
+ * same gradients as m3_ssd_backward_seq (kernels/mamba3_ssd.cu:558-808).
+ * The states entering each 32-step chunk are recomputed into the workspace, so
+ * the forward saves nothing.
+ *   inputs as for the forward, plus dy [B,T,nh*hd] (storage dtype)
+ *   dx [B,T,nh*hd] storage dtype (overwritten); dK, dQ [B,T,nh,N] f32 (overwritten)
+ *   d_adt, d_dt, d_trap [B,T,nh] f32 (overwritten; d_dt is the direct path only,
+ *   the caller adds A * d_adt as the reference does); dD [nh] f32, +=
+ * hd <= 64, N <= 128.
+ */
+typedef struct mamba_b200_m3_ssd_bwd_args {
+    int dtype;
+    int B, T, nh, hd, N;
+    const void* x;
+    const void* K;
+    const void* Q;
+    const float* dt;
+    const float* trap;
+    const float* adt;
+    const float* Dh;
+    const void* dy;
+    void* dx;
+    float* dK;
+    float* dQ;
+    float* d_adt;
+    float* d_dt;
+    float* d_trap;
+    float* dD;
+    void* workspace;           /* 256-byte aligned */
+    long long workspace_bytes; /* >= mamba_b200_m3_ssd_bwd_workspace_bytes(...) */
+} mamba_b200_m3_ssd_bwd_args;
+
+MAMBA_B200_API long long mamba_b200_m3_ssd_bwd_workspace_bytes(int B, int T, int nh, int hd, int N);
+MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream, const mamba_b200_m3_ssd_bwd_args* args);
+
+/*
  * conv1d backward for callers that cannot allocate: identical to
  * mamba_b200_conv1d_bwd, except that the partial-sum scratch is a fixed 16 MiB
  * array inside the library (workspace / workspace_bytes in `args` are ignored).

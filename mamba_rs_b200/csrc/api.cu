@@ -42,6 +42,7 @@ bool make_tmap_3d(Ctx* c, CUtensorMap* map, int dtype, const void* base, long lo
 int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limits
 int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
 int m3_configure(Ctx* c);       // m3_ssd.cu
+int m3_bwd_configure(Ctx* c);   // m3_ssd_bwd.cu
 
 }  // namespace mb200
 
@@ -76,6 +77,8 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     rc = m1_bwd_configure(c);
     if (rc) return rc;
     rc = m3_configure(c);
+    if (rc) return rc;
+    rc = m3_bwd_configure(c);
     if (rc) return rc;
 #endif
     return MAMBA_B200_OK;

@@ -184,7 +184,7 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-// 3-D tiled TMA load global -> this CTA's shared memory (no multicast).
+// 3-D tiled TMA load global -> this CTA's own shared memory.
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2) {
     asm volatile(

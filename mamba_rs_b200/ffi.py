@@ -93,6 +93,17 @@ class M3SsdArgs(C.Structure):
     ]
 
 
+class M3SsdBwdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("B", C.c_int), ("T", C.c_int), ("nh", C.c_int), ("hd", C.c_int), ("N", C.c_int),
+        ("x", C.c_void_p), ("K", C.c_void_p), ("Q", C.c_void_p),
+        ("dt", C.c_void_p), ("trap", C.c_void_p), ("adt", C.c_void_p), ("Dh", C.c_void_p),
+        ("dy", C.c_void_p), ("dx", C.c_void_p), ("dK", C.c_void_p), ("dQ", C.c_void_p),
+        ("d_adt", C.c_void_p), ("d_dt", C.c_void_p), ("d_trap", C.c_void_p), ("dD", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong),
+    ]
+
+
 _lib = None
 
 
@@ -131,6 +142,8 @@ def lib() -> C.CDLL:
         bind("mamba_b200_conv1d_bwd_static", [vp, vp, C.POINTER(Conv1dArgs)])
         bind("mamba_b200_conv1d_bwd_static_max_bytes", [], C.c_longlong)
         bind("mamba_b200_m3_ssd_fwd", [vp, vp, C.POINTER(M3SsdArgs)])
+        bind("mamba_b200_m3_ssd_bwd", [vp, vp, C.POINTER(M3SsdBwdArgs)])
+        bind("mamba_b200_m3_ssd_bwd_workspace_bytes", [C.c_int] * 5, C.c_longlong)
     return _lib
 
 

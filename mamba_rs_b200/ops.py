@@ -16,7 +16,7 @@ import torch
 from . import ffi
 
 __all__ = ["selective_scan_fwd", "selective_scan_bwd", "selective_scan_bwd_workspace_bytes",
-           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "dtype_code"]
+           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -283,3 +283,45 @@ def m3_ssd_fwd(x, K, Q, dt, trap, adt, Dh, *, ssm_state=None, k_state=None, v_st
         rc = ffi.lib().mamba_b200_m3_ssd_fwd(h.ptr, _stream(dev), C.byref(a))
     h.check(rc, "mamba_b200_m3_ssd_fwd")
     return y
+
+
+def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy, *, dD=None, workspace=None, handle=None):
+    """Mamba-3 SISO SSD backward for a window that started from a zero state.
+    Returns dx (storage dtype), dK, dQ, d_adt, d_dt, d_trap (f32) and dD (f32,
+    accumulated into the tensor passed in, or a fresh zero one).  d_dt is the
+    direct path only; the caller adds A * d_adt (src/mamba3_siso/gpu/backward.rs:420-457)."""
+    _require_cuda(x, K, Q, dt, trap, adt, Dh, dy, dD, workspace)
+    Bsz, T, nh, N = K.shape
+    hd = x.shape[2] // nh
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    for t, nm in ((x, "x"), (K, "K"), (Q, "Q"), (dy, "dy")):
+        if not t.is_contiguous() or t.dtype != x.dtype:
+            raise ValueError(f"{nm} must be contiguous and share x's dtype")
+    for t, nm in ((dt, "dt"), (trap, "trap"), (adt, "adt"), (Dh, "Dh"), (dD, "dD")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError(f"{nm} must be contiguous float32")
+    need = ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes(Bsz, T, nh, hd, N)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    dx = torch.empty_like(x)
+    dK = torch.empty((Bsz, T, nh, N), **f32)
+    dQ = torch.empty((Bsz, T, nh, N), **f32)
+    d_adt = torch.empty((Bsz, T, nh), **f32)
+    d_dt = torch.empty((Bsz, T, nh), **f32)
+    d_trap = torch.empty((Bsz, T, nh), **f32)
+    if dD is None:
+        dD = torch.zeros(nh, **f32)
+    a = ffi.M3SsdBwdArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.T, a.nh, a.hd, a.N = Bsz, T, nh, hd, N
+    a.x, a.K, a.Q, a.dy = _ptr(x), _ptr(K), _ptr(Q), _ptr(dy)
+    a.dt, a.trap, a.adt, a.Dh = _ptr(dt), _ptr(trap), _ptr(adt), _ptr(Dh)
+    a.dx, a.dK, a.dQ = _ptr(dx), _ptr(dK), _ptr(dQ)
+    a.d_adt, a.d_dt, a.d_trap, a.dD = _ptr(d_adt), _ptr(d_dt), _ptr(d_trap), _ptr(dD)
+    a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_m3_ssd_bwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_m3_ssd_bwd")
+    return dict(dx=dx, dK=dK, dQ=dQ, d_adt=d_adt, d_dt=d_dt, d_trap=d_trap, dD=dD)

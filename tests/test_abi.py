@@ -39,7 +39,7 @@ def test_args_struct_matches_c_layout():
     with the ctypes Structure (what a Rust #[repr(C)] mirror must also match)."""
     structs = {"mamba_b200_sscan_fwd_args": ffi.SscanFwdArgs}
     for extra in ("mamba_b200_sscan_bwd_args", "mamba_b200_sscan_step_args",
-                  "mamba_b200_conv1d_args", "mamba_b200_m3_ssd_args"):
+                  "mamba_b200_conv1d_args", "mamba_b200_m3_ssd_args", "mamba_b200_m3_ssd_bwd_args"):
         cls = getattr(ffi, "".join(p.capitalize() for p in extra.replace("mamba_b200_", "").split("_")), None)
         if cls is not None and extra in open(HEADER).read():
             structs[extra] = cls
