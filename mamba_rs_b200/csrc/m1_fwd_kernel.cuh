@@ -26,6 +26,10 @@ namespace mb200 {
 
 constexpr int kKMax = 8;  // widest supported d_conv
 
+#ifndef MB200_FWD_F32BC
+#define MB200_FWD_F32BC 1
+#endif
+
 struct FwdParams {
     CUtensorMap tm_x, tm_dl, tm_z, tm_b, tm_c, tm_y;
     const void *x, *dl, *z, *bm, *cm;
@@ -50,15 +54,20 @@ struct FwdTraits {
     static constexpr int DT = THREADS / LPC;  // channels per CTA (one lane group per channel)
     static constexpr int NP = NS * LPC;       // padded d_state
     static constexpr int STAGES = 3;
-    static constexpr bool kConvertBC = sizeof(Tact) != 4;
+    // 16-bit B / C are widened to f32 once per chunk and CTA (every lane of the
+    // CTA would otherwise repeat the widening at each step); large d_state keeps
+    // the storage dtype to bound shared memory.
+    static constexpr bool F32BC = MB200_FWD_F32BC && sizeof(Tact) == 2 && NS_ * LPC_ <= 64;
+    using Tbc = typename std::conditional<F32BC, float, Tact>::type;
     static constexpr size_t al(size_t v) { return (v + 127) & ~size_t(127); }
     static constexpr size_t RAW_ACT = al(sizeof(Tact) * TC * DT);
     static constexpr size_t RAW_BC = al(sizeof(Tact) * TC * NP);
     static constexpr size_t STAGE = 3 * RAW_ACT + 2 * RAW_BC;
     static constexpr size_t OFF_RAW = 0;
-    static constexpr size_t OFF_BS = OFF_RAW + STAGES * STAGE;  // B [TC][NP] zero-padded (N != NP only)
-    static constexpr size_t OFF_CS = OFF_BS + RAW_BC;           // C [TC][NP] zero-padded
-    static constexpr size_t OFF_OUT = OFF_CS + RAW_BC;          // 2 x Tact y [TC][DT]
+    static constexpr size_t BC_COPY = al(sizeof(Tbc) * TC * NP);
+    static constexpr size_t OFF_BS = OFF_RAW + STAGES * STAGE;  // B [TC][NP] widened / zero-padded copy
+    static constexpr size_t OFF_CS = OFF_BS + BC_COPY;          // C [TC][NP]
+    static constexpr size_t OFF_OUT = OFF_CS + BC_COPY;         // 2 x Tact y [TC][DT]
     static constexpr size_t OFF_HALO = OFF_OUT + 2 * RAW_ACT;                // f32 conv window [kKMax][DT]
     static constexpr size_t OFF_BAR = OFF_HALO + al(sizeof(float) * kKMax * DT);  // STAGES mbarriers
     static constexpr size_t SMEM = OFF_BAR + 128;
@@ -89,6 +98,12 @@ __device__ __forceinline__ void load_tile_plain(Tact* dst, const Tact* src, long
     }
 }
 
+template <typename To, typename Ti>
+__device__ __forceinline__ To bc_cast(Ti v) {
+    if constexpr (std::is_same<To, Ti>::value) return v;
+    else return to_f(v);
+}
+
 // FLAGS (compile-time, so that the hot block is one branch-free basic block):
 //   bit0 softplus on delta, bit1 gate present, bit2 conv1d + SiLU on x.
 template <typename Tr, typename Tact, int FLAGS>
@@ -100,8 +115,10 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
     constexpr int RB = Tr::RB, OWN = Tr::OWN;
     constexpr bool SHARE = Tr::SHARE;
     extern __shared__ __align__(128) unsigned char smem[];
-    Tact* Bs = reinterpret_cast<Tact*>(smem + Tr::OFF_BS);
-    Tact* Cs = reinterpret_cast<Tact*>(smem + Tr::OFF_CS);
+    using Tbc = typename Tr::Tbc;
+    constexpr bool F32BC = Tr::F32BC;
+    Tbc* Bs = reinterpret_cast<Tbc*>(smem + Tr::OFF_BS);
+    Tbc* Cs = reinterpret_cast<Tbc*>(smem + Tr::OFF_CS);
     float* halo = reinterpret_cast<float*>(smem + Tr::OFF_HALO);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Tr::OFF_BAR);
 
@@ -269,18 +286,34 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         if (tx_bytes) mbar_wait(&bars[s], (c / STAGES) & 1, p.status);
         __syncthreads();
 
-        // B / C are read by the recurrence straight from the landed tile in their
-        // storage dtype (half the shared-memory traffic of an f32 copy).  Only a
-        // d_state that is not a whole number of lane slices needs a zero-padded copy.
+        // B / C: 16-bit tiles are widened to f32 once per chunk (F32BC); otherwise the
+        // recurrence reads the landed tile in its storage dtype, and only a d_state
+        // that is not a whole number of lane slices needs a zero-padded copy.
         const bool padded = N != NP;
-        if (padded) {
+        if (F32BC && !padded) {
+            const uint4* rb = reinterpret_cast<const uint4*>(raw_b(s));
+            const uint4* rc = reinterpret_cast<const uint4*>(raw_c(s));
+            for (int i = tid; i < TC * NP / 8; i += THREADS) {
+                StateVec<Tact, 8> vb, vc;
+                vb.load(reinterpret_cast<const Tact*>(rb + i));
+                vc.load(reinterpret_cast<const Tact*>(rc + i));
+                float4* ob = reinterpret_cast<float4*>(Bs) + 2 * i;
+                float4* oc = reinterpret_cast<float4*>(Cs) + 2 * i;
+                const float2 b0 = vb.pair(0), b1 = vb.pair(1), b2 = vb.pair(2), b3 = vb.pair(3);
+                const float2 c0 = vc.pair(0), c1 = vc.pair(1), c2 = vc.pair(2), c3 = vc.pair(3);
+                ob[0] = make_float4(b0.x, b0.y, b1.x, b1.y);
+                ob[1] = make_float4(b2.x, b2.y, b3.x, b3.y);
+                oc[0] = make_float4(c0.x, c0.y, c1.x, c1.y);
+                oc[1] = make_float4(c2.x, c2.y, c3.x, c3.y);
+            }
+            __syncthreads();
+        } else if (F32BC || padded) {
             const Tact* rb = raw_b(s);
             const Tact* rc = raw_c(s);
-            const Tact zero = from_f<Tact>(0.0f);
             for (int i = tid; i < TC * NP; i += THREADS) {
                 const int r = i / NP, n = i - r * NP;
-                Bs[i] = n < N ? rb[r * N + n] : zero;
-                Cs[i] = n < N ? rc[r * N + n] : zero;
+                Bs[i] = n < N ? bc_cast<Tbc>(rb[r * N + n]) : bc_cast<Tbc>(from_f<Tact>(0.0f));
+                Cs[i] = n < N ? bc_cast<Tbc>(rc[r * N + n]) : bc_cast<Tbc>(from_f<Tact>(0.0f));
             }
             __syncthreads();
         }
@@ -302,8 +335,8 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         const Tact* rz = raw_z(s) + col;
         const float* hl = halo + col;
         Tact* ot = out_tile(c & 1) + col;
-        const Tact* Bp = (padded ? Bs : raw_b(s)) + n0;
-        const Tact* Cp = (padded ? Cs : raw_c(s)) + n0;
+        const Tbc* Bp = ((F32BC || padded) ? Bs : reinterpret_cast<const Tbc*>(raw_b(s))) + n0;
+        const Tbc* Cp = ((F32BC || padded) ? Cs : reinterpret_cast<const Tbc*>(raw_c(s))) + n0;
 
         // Elementwise stage of one timestep (row r of the chunk).
         auto elem = [&](auto replay_tag, int r) -> Elem {
@@ -355,7 +388,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             constexpr bool RP = decltype(replay_tag)::value;
             constexpr int NB = decltype(nb_tag)::value;
             constexpr bool SH = SHARE && NB == RB;
-            StateVec<Tact, NS> Bq[NB], Cq[NB];
+            StateVec<Tbc, NS> Bq[NB], Cq[NB];
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
                 Bq[i].load(Bp + (r0 + i) * NP);
