@@ -291,7 +291,8 @@ def main():
             "config": {"workload": workload_name(), "storage_dtype": "bf16", "global_batch": world * B,
                        "seq_len": T, "tokens_per_s": world * B * T / (ms_per_step * 1e-3),
                        "parallelism": f"batch-sharded x{world}, no collective on the scan",
-                       "l2": "inputs+outputs per step (408 MB) exceed the 126 MB L2",
+                       "l2": (f"inputs+outputs per step ({by / 1e6:.0f} MB) exceed the 126 MB L2" if by > 126e6 else
+                              f"inputs+outputs per step ({by / 1e6:.0f} MB) fit the 126 MB L2: not a valid bench size"),
                        "a_neg": "S4D-real -(n+1): arithmetic-progression fast path (2 exp2 per step)"},
             "clocks": clocks, "gpu_launches": args.steps,
             "e2e": (None if args.no_e2e else

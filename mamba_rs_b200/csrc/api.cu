@@ -71,11 +71,16 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
         c->encode_tiled = fn;
     MB200_CUDA_CHECK(c, cudaMalloc(&c->d_status, sizeof(int)));
     MB200_CUDA_CHECK(c, cudaMemset(c->d_status, 0, sizeof(int)));
-    int rc = m1_fwd_configure(c);
+    int rc = MAMBA_B200_OK;
+#ifndef MB200_BWD_TUNING  // tuning builds link one kernel family only
+    rc = m1_fwd_configure(c);
     if (rc) return rc;
-#ifndef MB200_FWD_TUNING  // tuning builds link the forward kernels only
+#endif
+#ifndef MB200_FWD_TUNING
     rc = m1_bwd_configure(c);
     if (rc) return rc;
+#endif
+#if !defined(MB200_FWD_TUNING) && !defined(MB200_BWD_TUNING)
     rc = m3_configure(c);
     if (rc) return rc;
     rc = m3_bwd_configure(c);

@@ -1,7 +1,10 @@
 // Mamba-1 fused selective-scan backward (BPTT) for sm_100a, by recomputation.
 //
 // The training-mode forward saves only the state ENTERING each block of S
-// timesteps (S = save_stride, 32 or 64).  One warp owns
+// timesteps (S = save_stride, 32 or 64; 32 is the fast setting).  This file
+// holds the host entry point, the reducers and the one-lane-per-channel kernel
+// used for d_state <= 8; d_state 9..16 runs the two-lane kernel of
+// m1_bwd2_kernel.cuh.  In the one-lane kernel one warp owns
 // (sample b, 32 channels), one channel per lane with all d_state values in
 // registers, and walks the blocks from last to first:
 //   1. TMA brings the block's u, delta, z, dy, B, C tiles (double-buffered
@@ -21,32 +24,16 @@
 
 #include <type_traits>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "internal.h"
+#include "m1_bwd2_kernel.cuh"
 
 namespace mb200 {
 
 constexpr int kBwdSub = 16;   // sub-block length (h_t kept in shared memory)
 constexpr int kBwdSMax = 64;  // largest save_stride
-
-struct BwdParams {
-    CUtensorMap tm_u, tm_dl, tm_z, tm_dy, tm_b, tm_c, tm_du, tm_ddl, tm_dz;
-    const void *u, *dl, *z, *dy, *bm, *cm;
-    void *du, *ddl, *dz;
-    long long ld_u, ld_dl, ld_z, ld_dy, ld_bc, ld_du, ld_ddl, ld_dz;
-    const float *a_neg, *Dp, *chunk_states;
-    float *part_bc;  // [B][tiles][T][2N]
-    float *part_a;   // [B][D][N]
-    float *part_d;   // [B][D]
-    int B, T, D, N, S;
-    int z_mode;
-    unsigned tma_mask;  // bit per tensor map, in declaration order
-    int* status;
-};
-
-enum : unsigned {
-    kBU = 1, kBDl = 2, kBZ = 4, kBDy = 8, kBB = 16, kBC = 32, kBDu = 64, kBDdl = 128, kBDz = 256
-};
 
 template <typename Tact, int NS>
 struct BwdTraits {
@@ -62,19 +49,6 @@ struct BwdTraits {
     static constexpr size_t OFF_BAR = OFF_DLS + sizeof(float) * kBwdSMax * 32;
     static constexpr size_t SMEM = OFF_BAR + 128;
 };
-
-template <typename Tact>
-__device__ __forceinline__ void bwd_load_plain(Tact* dst, const Tact* src, long long ld, int b, int T,
-                                               int t0, int c0, int cols, int rows, int box_cols) {
-    const Tact zero = from_f<Tact>(0.0f);
-    for (int i = threadIdx.x; i < rows * box_cols; i += 32) {
-        int r = i / box_cols, c = i - r * box_cols;
-        int t = t0 + r, col = c0 + c;
-        Tact v = zero;
-        if (t < T && col < cols) v = src[(static_cast<long long>(b) * T + t) * ld + col];
-        dst[i] = v;
-    }
-}
 
 // FLAGS: bit0 softplus on delta, bit1 gate present.
 template <typename Tact, int NS, int FLAGS>
@@ -415,8 +389,6 @@ __global__ void bwd_reduce_params_kernel(const float* __restrict__ part_a,
     }
 }
 
-typedef void (*BwdKernelFn)(const BwdParams);
-
 template <typename Tact, int NS>
 static void fill_bwd(BwdKernelFn* f, size_t* smem) {
     f[0] = sscan_bwd_kernel<Tact, NS, 0>;
@@ -449,7 +421,42 @@ static const BwdTable& bwd_table() {
     return t;
 }
 
+// Two-lane kernels (8 < d_state <= 16): [dtype][stride index][flags].
+struct Bwd2Table {
+    BwdKernelFn fn[3][2][4];
+    size_t smem[3][2];
+};
+
+static const Bwd2Table& bwd2_table() {
+    static Bwd2Table t;
+    static bool init = false;
+    if (!init) {
+#ifdef MB200_BWD_TUNING  // bf16 only: the other dtypes alias it and must not be launched
+        bwd2_kernels_bf16(t.fn[MAMBA_B200_F32], t.smem[MAMBA_B200_F32]);
+        bwd2_kernels_bf16(t.fn[MAMBA_B200_F16], t.smem[MAMBA_B200_F16]);
+#else
+        bwd2_kernels_f32(t.fn[MAMBA_B200_F32], t.smem[MAMBA_B200_F32]);
+        bwd2_kernels_f16(t.fn[MAMBA_B200_F16], t.smem[MAMBA_B200_F16]);
+#endif
+        bwd2_kernels_bf16(t.fn[MAMBA_B200_BF16], t.smem[MAMBA_B200_BF16]);
+        init = true;
+    }
+    return t;
+}
+
 int m1_bwd_configure(Ctx* c) {
+    const Bwd2Table& t2 = bwd2_table();
+    for (int dt = 0; dt < 3; ++dt)
+        for (int si = 0; si < 2; ++si)
+            for (int f = 0; f < 4; ++f) {
+                MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(t2.fn[dt][si][f]),
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         static_cast<int>(t2.smem[dt][si])));
+                // many small CTAs per SM: ask for the largest shared-memory carve-out
+                MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(t2.fn[dt][si][f]),
+                                                         cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                         cudaSharedmemCarveoutMaxShared));
+            }
     const BwdTable& t = bwd_table();
     for (int dt = 0; dt < 3; ++dt)
         for (int v = 0; v < 3; ++v)
@@ -463,7 +470,9 @@ int m1_bwd_configure(Ctx* c) {
 static int bwd_ns(int N) { return N <= 4 ? 4 : (N <= 8 ? 8 : 16); }
 
 static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off_d, size_t* total) {
-    const size_t tiles = (D + 31) / 32, V = 2 * bwd_ns(N);
+    // channel tiles of the dB/dC partials: 16 channels per CTA for the two-lane
+    // kernel (d_state > 8), 32 for the one-lane kernel
+    const size_t tiles = N > 8 ? (D + 15) / 16 : (D + 31) / 32, V = 2 * bwd_ns(N);
     size_t bc = sizeof(float) * static_cast<size_t>(B) * tiles * T * V;
     bc = (bc + 255) & ~size_t(255);
     size_t a = sizeof(float) * static_cast<size_t>(B) * D * N;
@@ -529,24 +538,36 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.S = a.save_stride; p.z_mode = a.z_mode;
     p.status = c->d_status;
     const int S = a.save_stride;
+    // one lane per channel for d_state <= 8 (and on request, for comparison)
+    static const bool one_lane_env = getenv("MAMBA_B200_BWD_ONE_LANE") != nullptr;
+    const bool two_lane = a.N > 8 && !one_lane_env;
+    const int DT = two_lane ? 16 : 32;  // channels per CTA
     unsigned m = 0;
-    if (make_tmap_3d(c, &p.tm_u, a.dtype, a.u, a.ld_u, a.D, a.T, a.B, 32, S)) m |= kBU;
-    if (make_tmap_3d(c, &p.tm_dl, a.dtype, a.delta, a.ld_delta, a.D, a.T, a.B, 32, S)) m |= kBDl;
-    if (!a.z_mode || make_tmap_3d(c, &p.tm_z, a.dtype, a.z, a.ld_z, a.D, a.T, a.B, 32, S)) m |= kBZ;
-    if (make_tmap_3d(c, &p.tm_dy, a.dtype, a.dy, a.ld_dy, a.D, a.T, a.B, 32, S)) m |= kBDy;
+    if (make_tmap_3d(c, &p.tm_u, a.dtype, a.u, a.ld_u, a.D, a.T, a.B, DT, S)) m |= kBU;
+    if (make_tmap_3d(c, &p.tm_dl, a.dtype, a.delta, a.ld_delta, a.D, a.T, a.B, DT, S)) m |= kBDl;
+    if (!a.z_mode || make_tmap_3d(c, &p.tm_z, a.dtype, a.z, a.ld_z, a.D, a.T, a.B, DT, S)) m |= kBZ;
+    if (make_tmap_3d(c, &p.tm_dy, a.dtype, a.dy, a.ld_dy, a.D, a.T, a.B, DT, S)) m |= kBDy;
     if (make_tmap_3d(c, &p.tm_b, a.dtype, a.Bm, a.ld_bc, a.N, a.T, a.B, a.N, S)) m |= kBB;
     if (make_tmap_3d(c, &p.tm_c, a.dtype, a.Cm, a.ld_bc, a.N, a.T, a.B, a.N, S)) m |= kBC;
-    if (make_tmap_3d(c, &p.tm_du, a.dtype, a.d_u, a.ld_du, a.D, a.T, a.B, 32, S)) m |= kBDu;
-    if (make_tmap_3d(c, &p.tm_ddl, a.dtype, a.d_delta, a.ld_ddelta, a.D, a.T, a.B, 32, S)) m |= kBDdl;
-    if (!a.z_mode || make_tmap_3d(c, &p.tm_dz, a.dtype, a.d_z, a.ld_dz, a.D, a.T, a.B, 32, S)) m |= kBDz;
+    if (!two_lane) {  // the two-lane kernel stores its outputs from registers
+        if (make_tmap_3d(c, &p.tm_du, a.dtype, a.d_u, a.ld_du, a.D, a.T, a.B, DT, S)) m |= kBDu;
+        if (make_tmap_3d(c, &p.tm_ddl, a.dtype, a.d_delta, a.ld_ddelta, a.D, a.T, a.B, DT, S)) m |= kBDdl;
+        if (!a.z_mode || make_tmap_3d(c, &p.tm_dz, a.dtype, a.d_z, a.ld_dz, a.D, a.T, a.B, DT, S)) m |= kBDz;
+    }
     p.tma_mask = m;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const BwdTable& t = bwd_table();
     const int flags = (a.delta_softplus ? 1 : 0) | (a.z_mode ? 2 : 0);
-    const int tiles = (a.D + 31) / 32;
+    const int tiles = (a.D + DT - 1) / DT;
     dim3 grid(tiles, a.B);
-    t.fn[a.dtype][vi][flags]<<<grid, 32, t.smem[a.dtype][vi], st>>>(p);
+    if (two_lane) {
+        const Bwd2Table& t2 = bwd2_table();
+        const int si = S == 32 ? 0 : 1;
+        t2.fn[a.dtype][si][flags]<<<grid, 32, t2.smem[a.dtype][si], st>>>(p);
+    } else {
+        t.fn[a.dtype][vi][flags]<<<grid, 32, t.smem[a.dtype][vi], st>>>(p);
+    }
     MB200_CUDA_CHECK(c, cudaGetLastError());
     const long long nbc = static_cast<long long>(a.B) * a.T * 2 * ns;
     bwd_reduce_bc_kernel<<<static_cast<unsigned>((nbc + 255) / 256), 256, 0, st>>>(
