@@ -19,10 +19,12 @@
 // It replaces m3_extract_da_cs_sum, m3_dqkv (+ its dD reduce), and the parts of
 // m3_ddt_dtrap / m3_final_grads that belong to the scan
 // (kernels/mamba3_chunked.cu:439-1035; src/mamba3_siso/gpu/backward.rs:235-457).
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
 #include "internal.h"
+#include "m3_tc.cuh"
 
 namespace mb200 {
 
@@ -38,6 +40,7 @@ struct M3BwdParams {
     float *ws_dscl;    // [B,T,nh] dscale
     float *ws_dD;      // [B,nh]
     int B, T, nh, hd, N;
+    int* status;
 };
 
 template <typename Tact>
@@ -298,6 +301,543 @@ __global__ void m3_bwd_finish_kernel(const M3BwdParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core backward (16-bit storage, headdim 64, d_state 128): the same
+// chunked formulas with 128-step chunks, every product on tcgen05 with f32
+// accumulators in TMEM.  One CTA of 128 threads per (sample, head); thread t
+// owns step t of the chunk and TMEM lane t.
+//   A. forward over the chunks: S^T[n][p] lives in TMEM; a 16-bit copy of the
+//      state entering each chunk goes to the workspace in operand-tile order.
+//   B. backward over the chunks, three MMA groups per chunk:
+//      1. G = Q K^T, P = dY V^T, R' = (E o dY) S_in, W = K dS^T
+//         -> rows of M1 = mask(scale L o P), M2 = mask(scale L o G) to shared
+//            memory, row sums of X, <Q_t, R'_t>, W rows scaled by w in place,
+//            dS decayed by exp(dA_end) in place
+//      2. G^T, P^T (column sums of X and dscale), dQ = R' + M1 K, dV = wW + M2^T dY
+//      3. dK = M1^T Q, U = V dS, dS += Q^T (E o dY)
+// Operands are rounded to the storage dtype (M1, M2, E o dY, the state copies),
+// so results carry 16-bit rounding like the forward's tensor-core path.
+namespace tcb {
+using namespace tc;
+
+constexpr int CS = 128, HD = 64, NS = 128;
+constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kDS = 114688, kM1 = 131072,
+                   kM2 = 163840, kEdY = 196608, kVec = 212992;
+constexpr uint32_t kBar = kVec + 4 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
+constexpr uint32_t c0 = 0, c1 = 128, c2 = 256, c3 = 384, cDS = 448, kTmemCols = 512;
+constexpr uint32_t kStateTile = NS * HD * 2;  // bytes of one 16-bit state copy
+
+template <typename Th>
+__global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int T = p.T, nh = p.nh;
+    constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
+    float* dA = reinterpret_cast<float*>(smem + kVec);
+    float* scl = dA + 128;
+    float* gam = dA + 256;
+    float* red = dA + 384;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
+    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
+    const uint32_t sbase = smem_u32(smem);
+
+    if (tid == 0) {
+        for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tslot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tslot;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+    const Th* xg = static_cast<const Th*>(p.x);
+    const Th* Kg = static_cast<const Th*>(p.K);
+    const Th* Qg = static_cast<const Th*>(p.Q);
+    const Th* dyg = static_cast<const Th*>(p.dy);
+    Th* dxg = static_cast<Th*>(p.dx);
+    const float Dv = p.Dh[h];
+    const int nc = (T + CS - 1) / CS;
+    unsigned char* ws_st = reinterpret_cast<unsigned char*>(p.ws_states) +
+                           (static_cast<size_t>(b) * nh + h) * nc * kStateTile;
+    uint32_t ph[4] = {0, 0, 0, 0};
+    bool ok = true;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+    // per-row scalars of chunk c -> dA (inclusive cumsum), scl, gam in shared memory
+    auto load_scalars = [&](int t0, int nv, float& run_o, float& g_o, float& s_o) {
+        const int t = t0 + tid;
+        float a = 0.0f, g = 0.0f, s = 0.0f;
+        if (tid < nv) {
+            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+            a = p.adt[th];
+            g = p.dt[th] * p.trap[th];
+            s = g;
+            if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
+        }
+        float run = a;
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, run, m);
+            if (lane >= m) run += o;
+        }
+        if (lane == 31) red[warp] = run;
+        gam[tid] = g;
+        scl[tid] = s;
+        __syncthreads();
+        float off = 0.0f;
+        for (int w = 0; w < warp; ++w) off += red[w];
+        run += off;
+        dA[tid] = run;
+        __syncthreads();
+        run_o = run; g_o = g; s_o = s;
+    };
+    auto wait_bar = [&](int i) {
+        ok = mbar_wait(&bars[i], ph[i], p.status) && ok;
+        ph[i] ^= 1;
+        fence_after();
+    };
+    // sum over the CTA of one float per thread (result to every thread)
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+        __syncthreads();
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        return red[0] + red[1] + red[2] + red[3];
+    };
+
+    // ---------------- A. forward: 16-bit copies of the entering states ----------------
+    for (int c = 0; c < nc; ++c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const bool last = c + 1 == nc;
+        float run = 0.0f, g = 0.0f, s = 0.0f;
+        if (!last) {
+            load_scalars(t0, nv, run, g, s);
+            const float dA_end = dA[nv - 1];
+            const float wt = tid < nv ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
+            const int t = t0 + tid;
+            const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
+            const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+#pragma unroll
+            for (int j = 0; j < NS / 8; ++j) {
+                uint4 k = zero4;
+                if (tid < nv) k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
+                *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
+            }
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                uint4 v = zero4;
+                if (tid < nv) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
+                uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float2 f = unpack2<Th>(w4[q4]);
+                    w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
+                }
+                *reinterpret_cast<uint4*>(smem + kDY + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+        }
+        if (c > 0) {  // state entering chunk c: copy out, then decay for the update
+            const float e_end = last ? 0.0f : ex2(dA[nv - 1] * kLog2e);
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                float sv[32];
+                tmem_ld32(lane_addr + cDS + q2 * 32, sv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(ws_st + static_cast<size_t>(c) * kStateTile + chunk_off(tid, q2 * 4 + j, HD)) =
+                        make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
+                                   pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
+                if (!last) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sv[i] *= e_end;
+                    tmem_st32(lane_addr + cDS + q2 * 32, sv);
+                }
+            }
+        }
+        if (last) break;
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idS = instr_desc(fmt, 1, 1, 64);
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k)  // S^T[n][p] += sum_t K[t][n] (w V)[t][p]
+                mma(tmem + cDS, desc_mnmajor(sbase + kK, k, NS), desc_mnmajor(sbase + kDY, k, HD), idS, c > 0 || k > 0);
+            commit(&bars[3]);
+        }
+        wait_bar(3);
+    }
+    fence_before();
+    __syncthreads();  // state copies of this CTA are in global memory (read back below by the same CTA)
+    fence_after();
+
+    // ---------------- B. backward over the chunks ----------------
+    bool has_ds = false;
+    float dD_acc = 0.0f;
+    for (int c = nc - 1; c >= 0; --c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const int t = t0 + tid;
+        const bool row_ok = tid < nv;
+        const bool has_sin = c > 0;
+        float run, g_t, s_t;
+        load_scalars(t0, nv, run, g_t, s_t);
+        const float dA_t = run, dA_end = dA[nv - 1];
+        const float e_t = ex2(dA_t * kLog2e), e_end = ex2(dA_end * kLog2e);
+        const float lend_t = row_ok ? ex2((dA_end - dA_t) * kLog2e) : 0.0f;
+        const float w_t = lend_t * s_t;
+        const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
+        const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+        // ---- loads: rows of Q, K, V, dY, E o dY; the entering state's tile ----
+#pragma unroll
+        for (int j = 0; j < NS / 8; ++j) {
+            uint4 q = zero4, k = zero4;
+            if (row_ok) {
+                q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
+                k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
+            }
+            *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = q;
+            *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
+        }
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            uint4 v = zero4, dyv = zero4;
+            if (row_ok) {
+                v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
+                dyv = *reinterpret_cast<const uint4*>(dyg + x_row + 8 * j);
+            }
+            *reinterpret_cast<uint4*>(smem + kV + chunk_off(tid, j, HD)) = v;
+            *reinterpret_cast<uint4*>(smem + kDY + chunk_off(tid, j, HD)) = dyv;
+            uint32_t w4[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float2 f = unpack2<Th>(w4[q4]);
+                w4[q4] = pack2<Th>(f.x * e_t, f.y * e_t);
+            }
+            *reinterpret_cast<uint4*>(smem + kEdY + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
+        if (has_sin) {
+            const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(smem + kSin + (j * 128 + tid) * 16) = src[j * 128 + tid];
+        }
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        // ---- group 1 ----
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idW = instr_desc(fmt, 0, 1, 64);
+#pragma unroll
+            for (int k = 0; k < NS / 16; ++k)  // G[t][s] = sum_n Q[t][n] K[s][n]
+                mma(tmem + c0, desc_kmajor(sbase + kQ, k, NS), desc_kmajor(sbase + kK, k, NS), idKK, k > 0);
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k)  // P[t][s] = sum_p dY[t][p] V[s][p]
+                mma(tmem + c1, desc_kmajor(sbase + kDY, k, HD), desc_kmajor(sbase + kV, k, HD), idKK, k > 0);
+            if (has_sin) {
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)  // R'[t][n] = sum_p (E dY)[t][p] S_in^T[n][p]
+                    mma(tmem + c2, desc_kmajor(sbase + kEdY, k, HD), desc_kmajor(sbase + kSin, k, HD), idKK, k > 0);
+            }
+            if (has_ds) {
+#pragma unroll
+                for (int k = 0; k < NS / 16; ++k)  // W[s][p] = sum_n K[s][n] dS^T[n][p]
+                    mma(tmem + c3, desc_kmajor(sbase + kK, k, NS), desc_mnmajor(sbase + kDS, k, HD), idW, k > 0);
+            }
+            commit(&bars[0]);
+        }
+        wait_bar(0);
+        // ---- epilogue 1 ----
+        float rowX = 0.0f, gd = 0.0f, pd = 0.0f, qr = 0.0f, ds_part = 0.0f;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            float gv[32], pv[32];
+            tmem_ld32(lane_addr + c0 + q4 * 32, gv);
+            tmem_ld32(lane_addr + c1 + q4 * 32, pv);
+            uint32_t pk1[16], pk2[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float m1[2], m2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int s = q4 * 32 + i + u;
+                    float a1 = 0.0f, a2v = 0.0f;
+                    if (s < tid && row_ok) {
+                        const float f = scl[s] * ex2((dA_t - dA[s]) * kLog2e);
+                        a1 = f * pv[i + u];
+                        a2v = f * gv[i + u];
+                        rowX = fmaf(a1, gv[i + u], rowX);
+                    } else if (s == tid) {
+                        gd = gv[i + u];
+                        pd = pv[i + u];
+                    }
+                    m1[u] = a1;
+                    m2[u] = a2v;
+                }
+                pk1[i / 2] = pack2<Th>(m1[0], m1[1]);
+                pk2[i / 2] = pack2<Th>(m2[0], m2[1]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) =
+                    make_uint4(pk1[4 * j], pk1[4 * j + 1], pk1[4 * j + 2], pk1[4 * j + 3]);
+                *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) =
+                    make_uint4(pk2[4 * j], pk2[4 * j + 1], pk2[4 * j + 2], pk2[4 * j + 3]);
+            }
+        }
+        if (!row_ok) gd = pd = 0.0f;
+        if (has_sin) {  // <Q_t, R'_t> (E_t is already inside R')
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                float rv[32];
+                tmem_ld32(lane_addr + c2 + q4 * 32, rv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + chunk_off(tid, q4 * 4 + j, NS));
+                    const uint32_t w4[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 f = unpack2<Th>(w4[u]);
+                        qr = fmaf(f.x, rv[8 * j + 2 * u], qr);
+                        qr = fmaf(f.y, rv[8 * j + 2 * u + 1], qr);
+                    }
+                }
+            }
+        }
+        if (has_ds) {
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                float wv[32];
+                tmem_ld32(lane_addr + c3 + q2 * 32, wv);  // W row s = tid -> w_s W
+#pragma unroll
+                for (int i = 0; i < 32; ++i) wv[i] *= w_t;
+                tmem_st32(lane_addr + c3 + q2 * 32, wv);
+                float dv[32];
+                tmem_ld32(lane_addr + cDS + q2 * 32, dv);  // dS^T row n = tid
+                if (has_sin) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 sv = *reinterpret_cast<const uint4*>(smem + kSin + chunk_off(tid, q2 * 4 + j, HD));
+                        const uint32_t w4[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float2 f = unpack2<Th>(w4[u]);
+                            ds_part = fmaf(f.x, dv[8 * j + 2 * u], ds_part);
+                            ds_part = fmaf(f.y, dv[8 * j + 2 * u + 1], ds_part);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dv[i] *= e_end;
+                tmem_st32(lane_addr + cDS + q2 * 32, dv);
+            }
+        }
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        // ---- group 2 ----
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idQ = instr_desc(fmt, 0, 1, 128),
+                           idV = instr_desc(fmt, 1, 1, 64);
+#pragma unroll
+            for (int k = 0; k < NS / 16; ++k)  // G^T[s][t]
+                mma(tmem + c0, desc_kmajor(sbase + kK, k, NS), desc_kmajor(sbase + kQ, k, NS), idKK, k > 0);
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k)  // P^T[s][t]
+                mma(tmem + c1, desc_kmajor(sbase + kV, k, HD), desc_kmajor(sbase + kDY, k, HD), idKK, k > 0);
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k)  // dQ[t][n] (+)= sum_s M1[t][s] K[s][n]
+                mma(tmem + c2, desc_kmajor(sbase + kM1, k, CS), desc_mnmajor(sbase + kK, k, NS), idQ, has_sin || k > 0);
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k)  // dV[s][p] (+)= sum_t M2[t][s] dY[t][p]
+                mma(tmem + c3, desc_mnmajor(sbase + kM2, k, CS), desc_mnmajor(sbase + kDY, k, HD), idV, has_ds || k > 0);
+            commit(&bars[1]);
+        }
+        wait_bar(1);
+        // ---- epilogue 2 ----
+        float dsc = 0.0f;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            float gv[32], pv[32];
+            tmem_ld32(lane_addr + c0 + q4 * 32, gv);
+            tmem_ld32(lane_addr + c1 + q4 * 32, pv);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int tt = q4 * 32 + i;
+                if (tt > tid && tt < nv) dsc = fmaf(ex2((dA[tt] - dA_t) * kLog2e) * gv[i], pv[i], dsc);
+            }
+        }
+        {
+            const float gp = g_t * pd;  // gamma_t P_tt
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                float av[32];
+                tmem_ld32(lane_addr + c2 + q4 * 32, av);
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + chunk_off(tid, q4 * 4 + j, NS));
+                        const uint32_t w4[4] = {kv.x, kv.y, kv.z, kv.w};
+                        float o[8];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float2 f = unpack2<Th>(w4[u]);
+                            o[2 * u] = fmaf(gp, f.x, av[8 * j + 2 * u]);
+                            o[2 * u + 1] = fmaf(gp, f.y, av[8 * j + 2 * u + 1]);
+                        }
+                        float4* dst = reinterpret_cast<float4*>(p.dQ + qk_row + q4 * 32 + 8 * j);
+                        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+                    }
+                }
+            }
+            const float dcoef = fmaf(g_t, gd, Dv);  // gamma_s G_ss + D
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                float av[32];
+                tmem_ld32(lane_addr + c3 + q2 * 32, av);
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 yv = *reinterpret_cast<const uint4*>(smem + kDY + chunk_off(tid, q2 * 4 + j, HD));
+                        const uint32_t w4[4] = {yv.x, yv.y, yv.z, yv.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float2 f = unpack2<Th>(w4[u]);
+                            o[u] = pack2<Th>(fmaf(dcoef, f.x, av[8 * j + 2 * u]), fmaf(dcoef, f.y, av[8 * j + 2 * u + 1]));
+                        }
+                        *reinterpret_cast<uint4*>(dxg + x_row + q2 * 32 + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+        }
+        fence_before();
+        __syncthreads();
+        // ---- group 3 ----
+        if (tid == 0) {
+            fence_after();
+            const uint32_t idK = instr_desc(fmt, 1, 1, 128), idU = instr_desc(fmt, 0, 0, 128),
+                           idS = instr_desc(fmt, 1, 1, 64);
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k)  // dK[s][n] = sum_t M1[t][s] Q[t][n]
+                mma(tmem + c0, desc_mnmajor(sbase + kM1, k, CS), desc_mnmajor(sbase + kQ, k, NS), idK, k > 0);
+            if (has_ds) {
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)  // U[s][n] = sum_p V[s][p] dS^T[n][p]
+                    mma(tmem + c1, desc_kmajor(sbase + kV, k, HD), desc_kmajor(sbase + kDS, k, HD), idU, k > 0);
+            }
+#pragma unroll
+            for (int k = 0; k < CS / 16; ++k)  // dS^T[n][p] (+)= sum_t Q[t][n] (E dY)[t][p]
+                mma(tmem + cDS, desc_mnmajor(sbase + kQ, k, NS), desc_mnmajor(sbase + kEdY, k, HD), idS, has_ds || k > 0);
+            commit(&bars[2]);
+        }
+        wait_bar(2);
+        // ---- epilogue 3 ----
+        float zw = 0.0f;  // w_s <K_s, U_s>
+        {
+            const float gp = g_t * pd;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                float av[32], uv[32];
+                tmem_ld32(lane_addr + c0 + q4 * 32, av);
+                if (has_ds) tmem_ld32(lane_addr + c1 + q4 * 32, uv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + chunk_off(tid, q4 * 4 + j, NS));
+                    const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + chunk_off(tid, q4 * 4 + j, NS));
+                    const uint32_t q4w[4] = {qv.x, qv.y, qv.z, qv.w};
+                    const uint32_t k4w[4] = {kv.x, kv.y, kv.z, kv.w};
+                    float o[8];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 fq = unpack2<Th>(q4w[u]);
+                        const float2 fk = unpack2<Th>(k4w[u]);
+                        float o0 = fmaf(gp, fq.x, av[8 * j + 2 * u]), o1 = fmaf(gp, fq.y, av[8 * j + 2 * u + 1]);
+                        if (has_ds) {
+                            const float u0 = w_t * uv[8 * j + 2 * u], u1 = w_t * uv[8 * j + 2 * u + 1];
+                            o0 += u0;
+                            o1 += u1;
+                            zw = fmaf(fk.x, u0, zw);
+                            zw = fmaf(fk.y, u1, zw);
+                        }
+                        o[2 * u] = o0;
+                        o[2 * u + 1] = o1;
+                    }
+                    if (row_ok) {
+                        float4* dst = reinterpret_cast<float4*>(p.dK + qk_row + q4 * 32 + 8 * j);
+                        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+                    }
+                }
+            }
+        }
+        // 16-bit copy of the new dS for the next (earlier) chunk
+        if (c > 0) {
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                float sv[32];
+                tmem_ld32(lane_addr + cDS + q2 * 32, sv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(smem + kDS + chunk_off(tid, q2 * 4 + j, HD)) =
+                        make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
+                                   pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
+            }
+        }
+        // ---- per-step scalars ----
+        if (!row_ok) zw = 0.0f;
+        const float sum_zw = block_sum(zw);
+        const float ds_dot = block_sum(ds_part);
+        float v = row_ok ? rowX - s_t * dsc + qr - zw : 0.0f;
+        if (tid == nv - 1) v += sum_zw + e_end * ds_dot;
+        // d(adt_r) = sum_{t >= r} d(dA_t): reverse inclusive scan over the CTA
+        float rs = v;
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+            const float o = __shfl_down_sync(0xffffffffu, rs, m);
+            if (lane + m < 32) rs += o;
+        }
+        __syncthreads();
+        if (lane == 0) red[warp] = rs;
+        __syncthreads();
+        for (int w = warp + 1; w < 4; ++w) rs += red[w];
+        if (row_ok) {
+            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+            p.d_adt[th] = rs;
+            p.ws_dgam[th] = gd * pd;
+            p.ws_dscl[th] = dsc + (s_t > 0.0f ? zw / s_t : 0.0f);
+            dD_acc += pd;
+        }
+        has_ds = true;
+        fence_proxy_async();
+        fence_before();
+        __syncthreads();
+        fence_after();
+    }
+    {
+        const float tot = block_sum(dD_acc);
+        if (tid == 0) p.ws_dD[static_cast<long long>(b) * nh + h] = tot;
+    }
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    (void)ok;
+}
+
+}  // namespace tcb
+
 static size_t m3_bwd_smem(int hd, int N) {
     const size_t LQ = N + 1, LV = hd + 1, LG = kM3C + 1;
     return sizeof(float) * (3 * kM3C * LQ + 3 * kM3C * LV + 2 * kM3C * LG + 2 * hd * LQ + 12 * 32);
@@ -320,6 +860,10 @@ int m3_bwd_configure(Ctx* c) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(m3_ssd_bwd_kernel<__nv_bfloat16>),
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tcb::m3_ssd_bwd_tc_kernel<__half>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tcb::kSmem));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tcb::kSmem));
     return MAMBA_B200_OK;
 }
 
@@ -366,10 +910,19 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     p.ws_dscl = reinterpret_cast<float*>(ws + o_s);
     p.ws_dD = reinterpret_cast<float*>(ws + o_d);
     p.B = a.B; p.T = a.T; p.nh = a.nh; p.hd = a.hd; p.N = a.N;
+    p.status = c->d_status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(a.nh, a.B);
     const size_t smem = m3_bwd_smem(a.hd, a.N);
-    if (a.dtype == MAMBA_B200_F32) m3_ssd_bwd_kernel<float><<<grid, 256, smem, st>>>(p);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    static const bool cuda_cores_env = getenv("MAMBA_B200_M3_BWD_CUDA_CORES") != nullptr;
+    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd == tcb::HD && a.N == tcb::NS && !cuda_cores_env &&
+                             al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) &&
+                             al16(a.dQ);
+    if (tensor_core) {
+        if (a.dtype == MAMBA_B200_F16) tcb::m3_ssd_bwd_tc_kernel<__half><<<grid, 128, tcb::kSmem, st>>>(p);
+        else tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16><<<grid, 128, tcb::kSmem, st>>>(p);
+    } else if (a.dtype == MAMBA_B200_F32) m3_ssd_bwd_kernel<float><<<grid, 256, smem, st>>>(p);
     else if (a.dtype == MAMBA_B200_F16) m3_ssd_bwd_kernel<__half><<<grid, 256, smem, st>>>(p);
     else m3_ssd_bwd_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(p);
     MB200_CUDA_CHECK(c, cudaGetLastError());
