@@ -126,9 +126,11 @@ constexpr uint32_t kSmem = kTmemSlot + 16;
 constexpr uint32_t cG = 0, cY1 = 128, cY2 = 192, cS = 256, kTmemCols = 512;
 
 template <typename Th>
-__global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
+__global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5;
+    // two threads per step: thread (row, half) owns row `row` of the chunk (TMEM lane
+    // `row`) and half of that row's columns in every elementwise stage
+    const int tid = threadIdx.x & 127, half = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3;
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = p.T, nh = p.nh;
     constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
@@ -139,12 +141,12 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
     const uint32_t sbase = smem_u32(smem);
 
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         fence_barrier_init();
     }
-    if (warp == 0) {
+    if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tslot)),
                      "r"(kTmemCols)
                      : "memory");
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
             const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
             const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
 #pragma unroll
-            for (int j = 0; j < NS / 8; ++j) {
+            for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
                 uint4 q = zero, k = zero;
                 if (row_ok) {
                     q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
             const float dA_end = dA[nv - 1];
             const float wt = row_ok ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
 #pragma unroll
-            for (int j = 0; j < HD / 8; ++j) {
+            for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
                 uint4 v = zero;
                 if (row_ok) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
                 *reinterpret_cast<uint4*>(smem + kV + chunk_off(tid, j, HD)) = v;
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
         fence_before();
         __syncthreads();
         // ---- 2. G = Q K^T (and Y2 = Q S_in^T for c > 0) ----
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idG = instr_desc(fmt, 0, 0, 128), idY = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
         {
             const float dAt = dA[tid], gt = gam[tid];
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float g[32];
                 tmem_ld32(lane_addr + cG + q4 * 32, g);
                 uint32_t packed[16];
@@ -277,8 +279,8 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
             }
             if (c > 0) {  // S^T row `tid` (state index n = tid) *= exp(dA_end)
                 const float e_end = ex2(dA[nv - 1] * kLog2e);
-#pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2) {
+                {
+                    const int q2 = half;
                     float sv[32];
                     tmem_ld32(lane_addr + cS + q2 * 32, sv);
 #pragma unroll
@@ -291,7 +293,7 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
         fence_before();
         __syncthreads();
         // ---- 4. Y1 = M V ;  S^T += K^T (w o V) ----
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idY = instr_desc(fmt, 0, 1, 64), idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
@@ -314,8 +316,8 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
         {
             const float e_t = ex2(dA[tid] * kLog2e);
             const long long y_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            {
+                const int q2 = half;
                 float y1[32], y2[32];
                 tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
                 if (c > 0) {
@@ -352,12 +354,13 @@ __global__ void __launch_bounds__(128) m3_ssd_fwd_tc_kernel(const M3Params p) {
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
         const long long last = static_cast<long long>(b) * T + (T - 1);
-        if (p.k_state) p.k_state[(static_cast<long long>(b) * nh + h) * NS + tid] = to_f(Kg[(last * nh + h) * NS + tid]);
-        if (p.v_state && tid < HD)
+        if (p.k_state && half == 0)
+            p.k_state[(static_cast<long long>(b) * nh + h) * NS + tid] = to_f(Kg[(last * nh + h) * NS + tid]);
+        if (p.v_state && half == 0 && tid < HD)
             p.v_state[(static_cast<long long>(b) * nh + h) * HD + tid] = to_f(xg[last * nh * HD + h * HD + tid]);
     }
     __syncthreads();
-    if (warp == 0)
+    if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     (void)ok;
 }
@@ -417,9 +420,9 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
     if (tensor_core) {
         dim3 grid(a.nh, a.B);
         if (a.dtype == MAMBA_B200_BF16)
-            tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16><<<grid, 128, tc::kSmem, st>>>(p);
+            tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16><<<grid, 256, tc::kSmem, st>>>(p);
         else
-            tc::m3_ssd_fwd_tc_kernel<__half><<<grid, 128, tc::kSmem, st>>>(p);
+            tc::m3_ssd_fwd_tc_kernel<__half><<<grid, 256, tc::kSmem, st>>>(p);
     } else {
         if (a.dtype == MAMBA_B200_F32) launch_seq<float>(p, st);
         else if (a.dtype == MAMBA_B200_F16) launch_seq<__half>(p, st);
