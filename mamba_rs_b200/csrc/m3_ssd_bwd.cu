@@ -323,14 +323,16 @@ using namespace tc;
 constexpr int CS = 128, HD = 64, NS = 128;
 constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kDS = 114688, kM1 = 131072,
                    kM2 = 163840, kEdY = 196608, kVec = 212992;
-constexpr uint32_t kBar = kVec + 4 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
+// f32 vectors: dA, scl, gam, red (scratch), gdv, pdv, part[5]
+constexpr uint32_t kBar = kVec + 11 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
 constexpr uint32_t c0 = 0, c1 = 128, c2 = 256, c3 = 384, cDS = 448, kTmemCols = 512;
 constexpr uint32_t kStateTile = NS * HD * 2;  // bytes of one 16-bit state copy
 
 template <typename Th>
-__global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p) {
+__global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // two threads per step: (row tid, half) share TMEM lane tid and split its columns
+    const int tid = threadIdx.x & 127, half = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3, lane = tid & 31;
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = p.T, nh = p.nh;
     constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
@@ -338,15 +340,18 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     float* scl = dA + 128;
     float* gam = dA + 256;
     float* red = dA + 384;
+    float* gdv = dA + 512;
+    float* pdv = dA + 640;
+    float* part = dA + 768;  // [5][128]: partial sums of the upper-half threads
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
     const uint32_t sbase = smem_u32(smem);
 
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
         fence_barrier_init();
     }
-    if (warp == 0) {
+    if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tslot)),
                      "r"(kTmemCols)
                      : "memory");
@@ -405,11 +410,11 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         fence_after();
     };
     // sum over the CTA of one float per thread (result to every thread)
-    auto block_sum = [&](float v) {
+    auto block_sum = [&](float v) {  // callers pass 0 from the upper-half threads
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
         __syncthreads();
-        if (lane == 0) red[warp] = v;
+        if (lane == 0 && half == 0) red[warp] = v;
         __syncthreads();
         return red[0] + red[1] + red[2] + red[3];
     };
@@ -427,13 +432,13 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
             const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
             const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
 #pragma unroll
-            for (int j = 0; j < NS / 8; ++j) {
+            for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
                 uint4 k = zero4;
                 if (tid < nv) k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
                 *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
             }
 #pragma unroll
-            for (int j = 0; j < HD / 8; ++j) {
+            for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
                 uint4 v = zero4;
                 if (tid < nv) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
                 uint32_t w4[4] = {v.x, v.y, v.z, v.w};
@@ -447,8 +452,8 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         }
         if (c > 0) {  // state entering chunk c: copy out, then decay for the update
             const float e_end = last ? 0.0f : ex2(dA[nv - 1] * kLog2e);
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            {
+                const int q2 = half;
                 float sv[32];
                 tmem_ld32(lane_addr + cDS + q2 * 32, sv);
 #pragma unroll
@@ -467,7 +472,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         fence_proxy_async();
         fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
@@ -499,7 +504,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
         // ---- loads: rows of Q, K, V, dY, E o dY; the entering state's tile ----
 #pragma unroll
-        for (int j = 0; j < NS / 8; ++j) {
+        for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
             uint4 q = zero4, k = zero4;
             if (row_ok) {
                 q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
@@ -509,7 +514,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
             *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
         }
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
+        for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
             uint4 v = zero4, dyv = zero4;
             if (row_ok) {
                 v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
@@ -528,14 +533,14 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         if (has_sin) {
             const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = half * 4; j < half * 4 + 4; ++j)
                 *reinterpret_cast<uint4*>(smem + kSin + (j * 128 + tid) * 16) = src[j * 128 + tid];
         }
         fence_proxy_async();
         fence_before();
         __syncthreads();
         // ---- group 1 ----
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idW = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
@@ -559,8 +564,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         wait_bar(0);
         // ---- epilogue 1 ----
         float rowX = 0.0f, gd = 0.0f, pd = 0.0f, qr = 0.0f, ds_part = 0.0f;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
@@ -595,10 +599,12 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                     make_uint4(pk2[4 * j], pk2[4 * j + 1], pk2[4 * j + 2], pk2[4 * j + 3]);
             }
         }
-        if (!row_ok) gd = pd = 0.0f;
+        if ((tid >> 6) == half) {  // the diagonal lies in this thread's columns
+            gdv[tid] = row_ok ? gd : 0.0f;
+            pdv[tid] = row_ok ? pd : 0.0f;
+        }
         if (has_sin) {  // <Q_t, R'_t> (E_t is already inside R')
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float rv[32];
                 tmem_ld32(lane_addr + c2 + q4 * 32, rv);
 #pragma unroll
@@ -615,8 +621,8 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
             }
         }
         if (has_ds) {
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            {
+                const int q2 = half;
                 float wv[32];
                 tmem_ld32(lane_addr + c3 + q2 * 32, wv);  // W row s = tid -> w_s W
 #pragma unroll
@@ -646,7 +652,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         fence_before();
         __syncthreads();
         // ---- group 2 ----
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idQ = instr_desc(fmt, 0, 1, 128),
                            idV = instr_desc(fmt, 1, 1, 64);
@@ -666,9 +672,10 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         }
         wait_bar(1);
         // ---- epilogue 2 ----
+        gd = gdv[tid];
+        pd = pdv[tid];
         float dsc = 0.0f;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
@@ -680,8 +687,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         }
         {
             const float gp = g_t * pd;  // gamma_t P_tt
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float av[32];
                 tmem_ld32(lane_addr + c2 + q4 * 32, av);
                 if (row_ok) {
@@ -703,8 +709,8 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                 }
             }
             const float dcoef = fmaf(g_t, gd, Dv);  // gamma_s G_ss + D
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            {
+                const int q2 = half;
                 float av[32];
                 tmem_ld32(lane_addr + c3 + q2 * 32, av);
                 if (row_ok) {
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         fence_before();
         __syncthreads();
         // ---- group 3 ----
-        if (tid == 0) {
+        if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idK = instr_desc(fmt, 1, 1, 128), idU = instr_desc(fmt, 0, 0, 128),
                            idS = instr_desc(fmt, 1, 1, 64);
@@ -748,8 +754,7 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         float zw = 0.0f;  // w_s <K_s, U_s>
         {
             const float gp = g_t * pd;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float av[32], uv[32];
                 tmem_ld32(lane_addr + c0 + q4 * 32, av);
                 if (has_ds) tmem_ld32(lane_addr + c1 + q4 * 32, uv);
@@ -785,8 +790,8 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         }
         // 16-bit copy of the new dS for the next (earlier) chunk
         if (c > 0) {
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            {
+                const int q2 = half;
                 float sv[32];
                 tmem_ld32(lane_addr + cDS + q2 * 32, sv);
 #pragma unroll
@@ -798,10 +803,18 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         }
         // ---- per-step scalars ----
         if (!row_ok) zw = 0.0f;
-        const float sum_zw = block_sum(zw);
-        const float ds_dot = block_sum(ds_part);
-        float v = row_ok ? rowX - s_t * dsc + qr - zw : 0.0f;
-        if (tid == nv - 1) v += sum_zw + e_end * ds_dot;
+        // fold the upper-half threads' partial sums into the lower-half thread of the row
+        if (half == 1) {
+            part[tid] = rowX; part[128 + tid] = qr; part[256 + tid] = dsc; part[384 + tid] = zw; part[512 + tid] = ds_part;
+        }
+        __syncthreads();
+        if (half == 0) {
+            rowX += part[tid]; qr += part[128 + tid]; dsc += part[256 + tid]; zw += part[384 + tid]; ds_part += part[512 + tid];
+        }
+        const float sum_zw = block_sum(half == 0 ? zw : 0.0f);
+        const float ds_dot = block_sum(half == 0 ? ds_part : 0.0f);
+        float v = (row_ok && half == 0) ? rowX - s_t * dsc + qr - zw : 0.0f;
+        if (tid == nv - 1 && half == 0) v += sum_zw + e_end * ds_dot;
         // d(adt_r) = sum_{t >= r} d(dA_t): reverse inclusive scan over the CTA
         float rs = v;
 #pragma unroll
@@ -810,10 +823,10 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
             if (lane + m < 32) rs += o;
         }
         __syncthreads();
-        if (lane == 0) red[warp] = rs;
+        if (lane == 0 && half == 0) red[warp] = rs;
         __syncthreads();
         for (int w = warp + 1; w < 4; ++w) rs += red[w];
-        if (row_ok) {
+        if (row_ok && half == 0) {
             const long long th = (static_cast<long long>(b) * T + t) * nh + h;
             p.d_adt[th] = rs;
             p.ws_dgam[th] = gd * pd;
@@ -827,11 +840,11 @@ __global__ void __launch_bounds__(128) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         fence_after();
     }
     {
-        const float tot = block_sum(dD_acc);
-        if (tid == 0) p.ws_dD[static_cast<long long>(b) * nh + h] = tot;
+        const float tot = block_sum(half == 0 ? dD_acc : 0.0f);
+        if (threadIdx.x == 0) p.ws_dD[static_cast<long long>(b) * nh + h] = tot;
     }
     __syncthreads();
-    if (warp == 0)
+    if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     (void)ok;
 }
@@ -920,8 +933,8 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
                              al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) &&
                              al16(a.dQ);
     if (tensor_core) {
-        if (a.dtype == MAMBA_B200_F16) tcb::m3_ssd_bwd_tc_kernel<__half><<<grid, 128, tcb::kSmem, st>>>(p);
-        else tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16><<<grid, 128, tcb::kSmem, st>>>(p);
+        if (a.dtype == MAMBA_B200_F16) tcb::m3_ssd_bwd_tc_kernel<__half><<<grid, 256, tcb::kSmem, st>>>(p);
+        else tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16><<<grid, 256, tcb::kSmem, st>>>(p);
     } else if (a.dtype == MAMBA_B200_F32) m3_ssd_bwd_kernel<float><<<grid, 256, smem, st>>>(p);
     else if (a.dtype == MAMBA_B200_F16) m3_ssd_bwd_kernel<__half><<<grid, 256, smem, st>>>(p);
     else m3_ssd_bwd_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(p);
