@@ -110,7 +110,7 @@ __global__ void m3_ssd_seq_kernel(const M3Params p) {
 }
 
 // ---------------------------------------------------------------------------
-// tcgen05 / TMEM chunked kernel.  hd = 64, N = 128, chunk = 128, 128 threads.
+// tcgen05 / TMEM chunked kernel.  hd = 64, N = 128, chunk = 128, 256 threads.
 // ---------------------------------------------------------------------------
 namespace tc {
 
@@ -118,12 +118,22 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // Shared-memory operand tiles: 8-row x 16-byte core matrices (no swizzle).  A
 // tile of R rows x C 16-bit columns keeps core (r/8, c/8) at
 // (r/8)*(C/8)*128 + (c/8)*128 bytes, row r%8 at +16*(r%8).
-constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kVw = 81920, kM = 98304, kS = 131072;
-constexpr uint32_t kVec = 147456;  // f32 dA[128], scale[128], gamma[128]
-constexpr uint32_t kBar = kVec + 3 * 128 * 4, kTmemSlot = kBar + 16;
+// Tiles: Q, two K and two V stages (the next chunk's rows land while this chunk
+// computes), w o V, M, the 16-bit state copy; then f32 vectors, barriers.
+constexpr uint32_t kQ = 0, kK = 32768, kV = 98304, kVw = 131072, kM = 147456, kS = 180224;
+constexpr uint32_t kKStage = 32768, kVStage = 16384;
+constexpr uint32_t kVec = 196608;  // f32 [2 stages][dA, scale, gamma][128]
+constexpr uint32_t kBar = kVec + 2 * 3 * 128 * 4, kTmemSlot = kBar + 16;
 constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns of the four f32 accumulators.
 constexpr uint32_t cG = 0, cY1 = 128, cY2 = 192, cS = 256, kTmemCols = 512;
+
+// 16-byte asynchronous copy global -> shared; `valid` false writes zeros.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(valid ? 16u : 0u)
+                 : "memory");
+}
 
 template <typename Th>
 __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
@@ -131,12 +141,11 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
     // two threads per step: thread (row, half) owns row `row` of the chunk (TMEM lane
     // `row`) and half of that row's columns in every elementwise stage
     const int tid = threadIdx.x & 127, half = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3;
+    const int lane = threadIdx.x & 31, wfull = threadIdx.x >> 5;
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = p.T, nh = p.nh;
     constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
-    float* dA = reinterpret_cast<float*>(smem + kVec);
-    float* scl = dA + 128;
-    float* gam = dA + 256;
+    float* vec = reinterpret_cast<float*>(smem + kVec);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
     const uint32_t sbase = smem_u32(smem);
@@ -166,57 +175,83 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
     const int nchunks = (T + CS - 1) / CS;
     bool ok = true;
 
+    // Cooperative tile loads: one warp instruction moves 8 rows x 64 bytes (whole
+    // 32-byte sectors in global memory, 512 contiguous bytes of the tile).
+    const int r8 = lane & 7, jc = lane >> 3;
+    auto issue_qk = [&](const Th* src, uint32_t tile, int c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int task = i * 8 + wfull, row = (task >> 2) * 8 + r8, j = (task & 3) * 4 + jc;
+            cp_async16(smem + tile + chunk_off(row, j, NS),
+                       src + ((static_cast<long long>(b) * T + t0 + min(row, nv - 1)) * nh + h) * NS + 8 * j, row < nv);
+        }
+    };
+    auto issue_v = [&](uint32_t tile, int c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int task = i * 8 + wfull, row = (task >> 1) * 8 + r8, j = (task & 1) * 4 + jc;
+            cp_async16(smem + tile + chunk_off(row, j, HD),
+                       xg + (static_cast<long long>(b) * T + t0 + min(row, nv - 1)) * nh * HD + h * HD + 8 * j, row < nv);
+        }
+    };
+    // Per-row scalars of chunk c into stage `st`: inclusive cumsum of adt, scale, gamma.
+    auto scalars = [&](int c, int st) {
+        float* dA = vec + st * 384;
+        float* scl = dA + 128;
+        float* gam = dA + 256;
+        const int t0 = c * CS, nv = min(CS, T - t0), t = t0 + tid;
+        float a = 0.0f, g = 0.0f, s = 0.0f;
+        if (tid < nv) {
+            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+            a = p.adt[th];
+            g = p.dt[th] * p.trap[th];
+            s = g;
+            if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
+        }
+        float run = a;
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, run, m);
+            if (lane >= m) run += o;
+        }
+        if (lane == 31) dA[warp] = run;  // slot reused below after the barrier
+        gam[tid] = g;
+        scl[tid] = s;
+        __syncthreads();
+        float off = 0.0f;
+        for (int w = 0; w < warp; ++w) off += dA[w];
+        __syncthreads();
+        dA[tid] = run + off;
+        __syncthreads();
+    };
+
+    if (nchunks > 0) {
+        issue_qk(Qg, kQ, 0);
+        issue_qk(Kg, kK, 0);
+        issue_v(kV, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        scalars(0, 0);
+    }
     for (int c = 0; c < nchunks; ++c) {
+        const int st = c & 1;
         const int t0 = c * CS, nv = min(CS, T - t0);
         const int t = t0 + tid;  // this thread's row
         const bool row_ok = tid < nv;
-        // ---- 1. load row `tid` of Q, K, V into the core-matrix tiles; per-row scalars ----
+        const float* dA = vec + st * 384;
+        const float* scl = dA + 128;
+        const float* gam = dA + 256;
+        const uint32_t tK = kK + st * kKStage, tV = kV + st * kVStage;
+        // ---- 1. this chunk's tiles have landed; w o V ----
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
         {
-            const uint4 zero = make_uint4(0, 0, 0, 0);
-            const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
-            const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
-#pragma unroll
-            for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
-                uint4 q = zero, k = zero;
-                if (row_ok) {
-                    q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
-                    k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
-                }
-                *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = q;
-                *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
-            }
-            float a = 0.0f, g = 0.0f, s = 0.0f;
-            if (row_ok) {
-                const long long th = (static_cast<long long>(b) * T + t) * nh + h;
-                a = p.adt[th];
-                g = p.dt[th] * p.trap[th];
-                s = g;
-                if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
-            }
-            // inclusive cumsum of adt over the chunk: warp scan + warp totals
-            float run = a;
-#pragma unroll
-            for (int m = 1; m < 32; m <<= 1) {
-                const float o = __shfl_up_sync(0xffffffffu, run, m);
-                if ((tid & 31) >= m) run += o;
-            }
-            if ((tid & 31) == 31) dA[warp] = run;  // slot reused below after the barrier
-            gam[tid] = g;
-            scl[tid] = s;
-            __syncthreads();
-            float off = 0.0f;
-            for (int w = 0; w < warp; ++w) off += dA[w];
-            __syncthreads();
-            run += off;
-            dA[tid] = run;
-            __syncthreads();
             const float dA_end = dA[nv - 1];
-            const float wt = row_ok ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
+            const float wt = row_ok ? ex2((dA_end - dA[tid]) * kLog2e) * scl[tid] : 0.0f;
 #pragma unroll
             for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                uint4 v = zero;
-                if (row_ok) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
-                *reinterpret_cast<uint4*>(smem + kV + chunk_off(tid, j, HD)) = v;
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + tV + chunk_off(tid, j, HD));
                 uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -234,27 +269,28 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
             fence_after();
             const uint32_t idG = instr_desc(fmt, 0, 0, 128), idY = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
-            for (int k = 0; k < NS / 16; ++k) {
-                const uint64_t a = smem_desc(sbase + kQ + k * 256, 128, 2048);
-                const uint64_t bb = smem_desc(sbase + kK + k * 256, 128, 2048);
-                mma(tmem + cG, a, bb, idG, k > 0);
-            }
+            for (int k = 0; k < NS / 16; ++k)
+                mma(tmem + cG, desc_kmajor(sbase + kQ, k, NS), desc_kmajor(sbase + tK, k, NS), idG, k > 0);
             if (c > 0) {
 #pragma unroll
-                for (int k = 0; k < NS / 16; ++k) {
-                    const uint64_t a = smem_desc(sbase + kQ + k * 256, 128, 2048);
-                    const uint64_t bb = smem_desc(sbase + kS + k * 2048, 1024, 128);  // N = p, K = n
-                    mma(tmem + cY2, a, bb, idY, k > 0);
-                }
+                for (int k = 0; k < NS / 16; ++k)  // N = p, K = n
+                    mma(tmem + cY2, desc_kmajor(sbase + kQ, k, NS), desc_mnmajor(sbase + kS, k, HD), idY, k > 0);
             }
             commit(&bars[0]);
         }
         ok = mbar_wait(&bars[0], c & 1, p.status) && ok;
         fence_after();
+        // Q is free again and the other K / V stage was last read a chunk ago: start
+        // the next chunk's loads under this chunk's remaining work.
+        if (c + 1 < nchunks) {
+            issue_qk(Qg, kQ, c + 1);
+            issue_qk(Kg, kK + (st ^ 1) * kKStage, c + 1);
+            issue_v(kV + (st ^ 1) * kVStage, c + 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         // ---- 3. decay / causal mask -> M (A operand of M V); rescale the running state ----
         {
             const float dAt = dA[tid], gt = gam[tid];
-#pragma unroll
             for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float g[32];
                 tmem_ld32(lane_addr + cG + q4 * 32, g);
@@ -279,14 +315,11 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
             }
             if (c > 0) {  // S^T row `tid` (state index n = tid) *= exp(dA_end)
                 const float e_end = ex2(dA[nv - 1] * kLog2e);
-                {
-                    const int q2 = half;
-                    float sv[32];
-                    tmem_ld32(lane_addr + cS + q2 * 32, sv);
+                float sv[32];
+                tmem_ld32(lane_addr + cS + half * 32, sv);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) sv[i] *= e_end;
-                    tmem_st32(lane_addr + cS + q2 * 32, sv);
-                }
+                for (int i = 0; i < 32; ++i) sv[i] *= e_end;
+                tmem_st32(lane_addr + cS + half * 32, sv);
             }
         }
         fence_proxy_async();
@@ -297,54 +330,47 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
             fence_after();
             const uint32_t idY = instr_desc(fmt, 0, 1, 64), idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
-            for (int k = 0; k < CS / 16; ++k) {
-                const uint64_t a = smem_desc(sbase + kM + k * 256, 128, 2048);
-                const uint64_t bb = smem_desc(sbase + kV + k * 2048, 1024, 128);  // N = p, K = s
-                mma(tmem + cY1, a, bb, idY, k > 0);
-            }
+            for (int k = 0; k < CS / 16; ++k)  // N = p, K = s
+                mma(tmem + cY1, desc_kmajor(sbase + kM, k, CS), desc_mnmajor(sbase + tV, k, HD), idY, k > 0);
 #pragma unroll
-            for (int k = 0; k < CS / 16; ++k) {
-                const uint64_t a = smem_desc(sbase + kK + k * 4096, 2048, 128);   // M = n, K = t
-                const uint64_t bb = smem_desc(sbase + kVw + k * 2048, 1024, 128);  // N = p, K = t
-                mma(tmem + cS, a, bb, idS, c > 0 || k > 0);
-            }
+            for (int k = 0; k < CS / 16; ++k)  // M = n, N = p, K = t
+                mma(tmem + cS, desc_mnmajor(sbase + tK, k, NS), desc_mnmajor(sbase + kVw, k, HD), idS, c > 0 || k > 0);
             commit(&bars[1]);
         }
+        if (c + 1 < nchunks) scalars(c + 1, st ^ 1);  // under the MMAs
         ok = mbar_wait(&bars[1], c & 1, p.status) && ok;
         fence_after();
         // ---- 5. epilogue: y row; 16-bit copy of the new state for the next chunk ----
         {
             const float e_t = ex2(dA[tid] * kLog2e);
             const long long y_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
-            {
-                const int q2 = half;
-                float y1[32], y2[32];
-                tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
-                if (c > 0) {
-                    tmem_ld32(lane_addr + cY2 + q2 * 32, y2);
+            const int q2 = half;
+            float y1[32], y2[32];
+            tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
+            if (c > 0) {
+                tmem_ld32(lane_addr + cY2 + q2 * 32, y2);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) y1[i] = fmaf(e_t, y2[i], y1[i]);
-                }
-                if (row_ok) {
+                for (int i = 0; i < 32; ++i) y1[i] = fmaf(e_t, y2[i], y1[i]);
+            }
+            if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
-                            make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
-                                       pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
-                }
-                float sv[32];
-                tmem_ld32(lane_addr + cS + q2 * 32, sv);
-                if (c + 1 < nchunks) {
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
+                        make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
+                                   pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
+            }
+            float sv[32];
+            tmem_ld32(lane_addr + cS + q2 * 32, sv);
+            if (c + 1 < nchunks) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(smem + kS + chunk_off(tid, q2 * 4 + j, HD)) =
-                            make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
-                                       pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
-                } else if (p.ssm_state) {  // final state [b, h, p, n], n = tid
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(smem + kS + chunk_off(tid, q2 * 4 + j, HD)) =
+                        make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
+                                   pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
+            } else if (p.ssm_state) {  // final state [b, h, p, n], n = tid
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        p.ssm_state[((static_cast<long long>(b) * nh + h) * HD + q2 * 32 + i) * NS + tid] = sv[i];
-                }
+                for (int i = 0; i < 32; ++i)
+                    p.ssm_state[((static_cast<long long>(b) * nh + h) * HD + q2 * 32 + i) * NS + tid] = sv[i];
             }
         }
         fence_before();
