@@ -118,15 +118,16 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // Shared-memory operand tiles: 8-row x 16-byte core matrices (no swizzle).  A
 // tile of R rows x C 16-bit columns keeps core (r/8, c/8) at
 // (r/8)*(C/8)*128 + (c/8)*128 bytes, row r%8 at +16*(r%8).
-// Tiles: Q, two K and two V stages (the next chunk's rows land while this chunk
-// computes), w o V, M, the 16-bit state copy; then f32 vectors, barriers.
-constexpr uint32_t kQ = 0, kK = 32768, kV = 98304, kVw = 131072, kM = 147456, kS = 180224;
-constexpr uint32_t kKStage = 32768, kVStage = 16384;
-constexpr uint32_t kVec = 196608;  // f32 [2 stages][dA, scale, gamma][128]
-constexpr uint32_t kBar = kVec + 2 * 3 * 128 * 4, kTmemSlot = kBar + 16;
+// Tiles, sized so that TWO CTAs share an SM (their load, MMA and epilogue
+// phases overlap each other): Q, reused for M once G is done; K; V; one tile
+// that holds w o V for the state update and then the 16-bit copy of the new
+// state for the next chunk's Y2; then f32 vectors, barriers.
+constexpr uint32_t kQ = 0, kM = 0, kK = 32768, kV = 65536, kVw = 81920, kS = 81920;
+constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128]
+constexpr uint32_t kBar = kVec + 3 * 128 * 4, kTmemSlot = kBar + 16;
 constexpr uint32_t kSmem = kTmemSlot + 16;
-// TMEM columns of the four f32 accumulators.
-constexpr uint32_t cG = 0, cY1 = 128, cY2 = 192, cS = 256, kTmemCols = 512;
+// TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
+constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
 
 // 16-byte asynchronous copy global -> shared; `valid` false writes zeros.
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -227,40 +228,21 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
         __syncthreads();
     };
 
-    if (nchunks > 0) {
-        issue_qk(Qg, kQ, 0);
-        issue_qk(Kg, kK, 0);
-        issue_v(kV, 0);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        scalars(0, 0);
-    }
     for (int c = 0; c < nchunks; ++c) {
-        const int st = c & 1;
         const int t0 = c * CS, nv = min(CS, T - t0);
         const int t = t0 + tid;  // this thread's row
         const bool row_ok = tid < nv;
-        const float* dA = vec + st * 384;
+        const float* dA = vec;
         const float* scl = dA + 128;
         const float* gam = dA + 256;
-        const uint32_t tK = kK + st * kKStage, tV = kV + st * kVStage;
-        // ---- 1. this chunk's tiles have landed; w o V ----
+        const uint32_t tK = kK, tV = kV;
+        // ---- 1. this chunk's Q, K, V tiles (asynchronous copies) and per-row scalars ----
+        issue_qk(Qg, kQ, c);
+        issue_qk(Kg, kK, c);
+        issue_v(kV, c);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        scalars(c, 0);
         asm volatile("cp.async.wait_all;" ::: "memory");
-        __syncthreads();
-        {
-            const float dA_end = dA[nv - 1];
-            const float wt = row_ok ? ex2((dA_end - dA[tid]) * kLog2e) * scl[tid] : 0.0f;
-#pragma unroll
-            for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(smem + tV + chunk_off(tid, j, HD));
-                uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const float2 f = unpack2<Th>(w4[q4]);
-                    w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
-                }
-                *reinterpret_cast<uint4*>(smem + kVw + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-            }
-        }
         fence_proxy_async();
         fence_before();
         __syncthreads();
@@ -280,16 +262,23 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
         }
         ok = mbar_wait(&bars[0], c & 1, p.status) && ok;
         fence_after();
-        // Q is free again and the other K / V stage was last read a chunk ago: start
-        // the next chunk's loads under this chunk's remaining work.
-        if (c + 1 < nchunks) {
-            issue_qk(Qg, kQ, c + 1);
-            issue_qk(Kg, kK + (st ^ 1) * kKStage, c + 1);
-            issue_v(kV + (st ^ 1) * kVStage, c + 1);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        // ---- 3. decay / causal mask -> M (A operand of M V); rescale the running state ----
+        // ---- 3. decay / causal mask -> M (over the Q tile); w o V (over the old state
+        //         copy); rescale the running state ----
         {
+            {
+                const float wt = row_ok ? ex2((dA[nv - 1] - dA[tid]) * kLog2e) * scl[tid] : 0.0f;
+#pragma unroll
+                for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(smem + tV + chunk_off(tid, j, HD));
+                    uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float2 f = unpack2<Th>(w4[q4]);
+                        w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
+                    }
+                    *reinterpret_cast<uint4*>(smem + kVw + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+            }
             const float dAt = dA[tid], gt = gam[tid];
             for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float g[32];
@@ -337,7 +326,6 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
                 mma(tmem + cS, desc_mnmajor(sbase + tK, k, NS), desc_mnmajor(sbase + kVw, k, HD), idS, c > 0 || k > 0);
             commit(&bars[1]);
         }
-        if (c + 1 < nchunks) scalars(c + 1, st ^ 1);  // under the MMAs
         ok = mbar_wait(&bars[1], c & 1, p.status) && ok;
         fence_after();
         // ---- 5. epilogue: y row; 16-bit copy of the new state for the next chunk ----
