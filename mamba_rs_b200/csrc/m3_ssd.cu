@@ -281,6 +281,12 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
             }
             const float dAt = dA[tid], gt = gam[tid];
             for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
+                if (q4 > warp) {  // wholly above the diagonal for every row of this warp
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) = make_uint4(0, 0, 0, 0);
+                    continue;
+                }
                 float g[32];
                 tmem_ld32(lane_addr + cG + q4 * 32, g);
                 uint32_t packed[16];

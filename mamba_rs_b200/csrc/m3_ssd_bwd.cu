@@ -565,6 +565,14 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         // ---- epilogue 1 ----
         float rowX = 0.0f, gd = 0.0f, pd = 0.0f, qr = 0.0f, ds_part = 0.0f;
         for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
+            if (q4 > warp) {  // wholly above the diagonal for every row of this warp
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
+                }
+                continue;
+            }
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
@@ -676,6 +684,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         pd = pdv[tid];
         float dsc = 0.0f;
         for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
+            if (q4 < warp) continue;  // only later steps (tt > s) contribute
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
