@@ -6,6 +6,8 @@
 // once (plus a K-1 row halo per time chunk).
 #include <string.h>
 
+#include <initializer_list>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -227,6 +229,241 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const ConvParams p) {
     pt[K] = db;
 }
 
+// ---------------------------------------------------------------------------
+// Vector variants (d_conv <= 4, rows and pointers aligned to the vector): a
+// thread owns VEC adjacent channels and moves them with one 8- or 16-byte
+// access per step, four steps of loads in flight.  Same arithmetic, in the same
+// order per channel, as the scalar kernels above.
+// ---------------------------------------------------------------------------
+constexpr int kConvKV = 4;     // widest d_conv of the vector kernels
+constexpr int kConvFwdTT = 64;  // timesteps per thread, forward
+
+template <typename Tact, int VEC>
+__device__ __forceinline__ void load_vec(const Tact* ptr, float* out) {
+    if (sizeof(Tact) * VEC == 16) {
+        const uint4 v = *reinterpret_cast<const uint4*>(ptr);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (sizeof(Tact) == 4) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = __uint_as_float(w[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const Tact* h = reinterpret_cast<const Tact*>(&w[i]);
+                out[2 * i] = to_f(h[0]);
+                out[2 * i + 1] = to_f(h[1]);
+            }
+        }
+    } else {  // 8 bytes: four 16-bit values
+        const uint2 v = *reinterpret_cast<const uint2*>(ptr);
+        const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const Tact* h = reinterpret_cast<const Tact*>(&w[i]);
+            out[2 * i] = to_f(h[0]);
+            out[2 * i + 1] = to_f(h[1]);
+        }
+    }
+}
+template <typename Tact, int VEC>
+__device__ __forceinline__ void store_vec(Tact* ptr, const float* v) {
+    __align__(16) Tact tmp[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) tmp[i] = from_f<Tact>(v[i]);
+    if (sizeof(Tact) * VEC == 16) *reinterpret_cast<uint4*>(ptr) = *reinterpret_cast<const uint4*>(tmp);
+    else *reinterpret_cast<uint2*>(ptr) = *reinterpret_cast<const uint2*>(tmp);
+}
+
+// Taps of VEC adjacent channels, right-aligned in KV slots (absent taps zero), and bias.
+template <int VEC>
+__device__ __forceinline__ void conv_load_taps(const ConvParams& p, int d, float (*w)[VEC], float* bias) {
+    constexpr int KV = kConvKV;
+    const int K = p.K;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 4) {
+        const float4 bv = *reinterpret_cast<const float4*>(p.bias + d + v);
+        bias[v] = bv.x; bias[v + 1] = bv.y; bias[v + 2] = bv.z; bias[v + 3] = bv.w;
+    }
+    if (K == KV) {  // one 16-byte load per channel
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const float4 wv = *reinterpret_cast<const float4*>(p.w + static_cast<long long>(d + v) * KV);
+            w[0][v] = wv.x; w[1][v] = wv.y; w[2][v] = wv.z; w[3][v] = wv.w;
+        }
+    } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+#pragma unroll
+            for (int k = 0; k < KV; ++k) {
+                const int kk = k - (KV - K);
+                w[k][v] = kk >= 0 ? p.w[static_cast<long long>(d + v) * K + kk] : 0.0f;
+            }
+    }
+}
+
+template <typename Tact>
+__global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) {
+    constexpr int VEC = 16 / sizeof(Tact), KV = kConvKV;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    const int t0 = blockIdx.y * kConvFwdTT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const int K = p.K;
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * p.T * p.ld_x + d;
+    Tact* ub = static_cast<Tact*>(p.u) + static_cast<long long>(b) * p.T * p.ld_u + d;
+    // taps right-aligned: w[KV-1] meets x[t], absent taps are zero
+    float w[KV][VEC], win[KV - 1][VEC], bias[VEC];
+    conv_load_taps<VEC>(p, d, w, bias);
+    if (t0 >= KV - 1) {  // history rows lie in x: whole-vector loads (absent taps have zero weight)
+#pragma unroll
+        for (int k = 0; k < KV - 1; ++k)
+            load_vec<Tact, VEC>(xb + static_cast<long long>(t0 - (KV - 1) + k) * p.ld_x, win[k]);
+    } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+#pragma unroll
+            for (int k = 0; k < KV - 1; ++k)
+                win[k][v] = k - (KV - K) >= 0 ? conv_x_at(p, xb + v, b, d + v, t0 - (KV - 1) + k) : 0.0f;
+    }
+    const int t1 = min(p.T, t0 + kConvFwdTT);
+    for (int tb = t0; tb < t1; tb += 4) {
+        float cur[4][VEC];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tb + i < t1) load_vec<Tact, VEC>(xb + static_cast<long long>(tb + i) * p.ld_x, cur[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tb + i < t1) {
+                float o[VEC];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    float acc = bias[v];
+#pragma unroll
+                    for (int k = 0; k < KV - 1; ++k) acc = fmaf(win[k][v], w[k][v], acc);
+                    acc = fmaf(cur[i][v], w[KV - 1][v], acc);
+                    o[v] = siluf_fast(acc);
+#pragma unroll
+                    for (int k = 0; k < KV - 2; ++k) win[k][v] = win[k + 1][v];
+                    win[KV - 2][v] = cur[i][v];
+                }
+                store_vec<Tact, VEC>(ub + static_cast<long long>(tb + i) * p.ld_u, o);
+            }
+        }
+    }
+}
+
+template <typename Tact>
+__global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) {
+    constexpr int VEC = 4, KV = kConvKV;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    const int chunk = blockIdx.y, t0 = chunk * kConvTT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const int K = p.K, T = p.T;
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * T * p.ld_x + d;
+    const Tact* gb = static_cast<const Tact*>(p.du) + static_cast<long long>(b) * T * p.ld_du + d;
+    Tact* dxb = static_cast<Tact*>(p.dx) + static_cast<long long>(b) * T * p.ld_dx + d;
+    // right-aligned taps as in the forward; win[k] = x[t - (KV-1) + k]
+    float w[KV][VEC], win[KV][VEC], dco[KV - 1][VEC], dW[KV][VEC], bias[VEC], db[VEC];
+    const int t1 = min(T, t0 + kConvTT);
+    const int t_start = min(T - 1, t1 + K - 2);
+    conv_load_taps<VEC>(p, d, w, bias);
+    if (t_start >= KV - 1) {
+#pragma unroll
+        for (int k = 0; k < KV; ++k)
+            load_vec<Tact, VEC>(xb + static_cast<long long>(t_start - (KV - 1) + k) * p.ld_x, win[k]);
+    } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+#pragma unroll
+            for (int k = 0; k < KV; ++k)
+                win[k][v] = k - (KV - K) >= 0 ? conv_x_at(p, xb + v, b, d + v, t_start - (KV - 1) + k) : 0.0f;
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        db[v] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            dW[k][v] = 0.0f;
+            if (k < KV - 1) dco[k][v] = 0.0f;
+        }
+    }
+    for (int tb = t_start; tb >= t0; tb -= 4) {
+        // loads of four steps: d_u[t] and the input that enters the window when it
+        // slides back past t (x[t - K], from the entering state when negative)
+        float g4[4][VEC], xin[4][VEC];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = tb - i;
+            if (t >= t0) {
+                load_vec<Tact, VEC>(gb + static_cast<long long>(t) * p.ld_du, g4[i]);
+                if (t - K >= 0) {
+                    load_vec<Tact, VEC>(xb + static_cast<long long>(t - K) * p.ld_x, xin[i]);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) xin[i][v] = conv_x_at(p, xb + v, b, d + v, t - K);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = tb - i;
+            if (t >= t0) {
+                float dxv[VEC];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    float acc = bias[v];
+#pragma unroll
+                    for (int k = 0; k < KV; ++k) acc = fmaf(win[k][v], w[k][v], acc);
+                    const float sg = sigmoidf_fast(acc);
+                    const float g = g4[i][v] * sg * fmaf(acc, 1.0f - sg, 1.0f);
+                    if (t < t1) {
+                        db[v] += g;
+                        float dx = g * w[KV - 1][v];
+#pragma unroll
+                        for (int k = 0; k < KV; ++k) dW[k][v] = fmaf(g, win[k][v], dW[k][v]);
+                        // future steps: dco[j] = dco[t + 1 + j] meets tap KV-2-j
+#pragma unroll
+                        for (int j = 0; j < KV - 1; ++j) dx = fmaf(dco[j][v], w[KV - 2 - j][v], dx);
+                        dxv[v] = dx;
+                    }
+#pragma unroll
+                    for (int j = KV - 2; j > 0; --j) dco[j][v] = dco[j - 1][v];
+                    dco[0][v] = g;
+#pragma unroll
+                    for (int k = KV - 1; k > 0; --k) win[k][v] = win[k - 1][v];
+                    // x[t - K] enters at the oldest tap that exists (slot KV - K)
+#pragma unroll
+                    for (int k = 0; k < KV; ++k)
+                        if (k == KV - K) win[k][v] = xin[i][v];
+                }
+                if (t < t1) store_vec<Tact, VEC>(dxb + static_cast<long long>(t) * p.ld_dx, dxv);
+            }
+        }
+    }
+    const int chunks = gridDim.y;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        float* pt = p.part + ((static_cast<long long>(b) * chunks + chunk) * p.D + d + v) * (K + 1);
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int kk = k - (KV - K);
+            if (kk >= 0) pt[kk] = dW[k][v];
+        }
+        pt[K] = db[v];
+    }
+}
+
+// The vector kernels need d_conv <= 4 and every row start on a vector boundary.
+static bool conv_vec_ok(int K, int D, int vec, size_t esize, std::initializer_list<const void*> ptrs,
+                        std::initializer_list<long long> lds) {
+    if (K > kConvKV || D % vec) return false;
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) % (vec * esize)) return false;
+    for (long long ld : lds)
+        if (ld % vec) return false;
+    return true;
+}
+
 // dW[D,K] += sum over (b, chunk) partials; db[D] likewise, in index order.
 __global__ void conv1d_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dW,
                                          float* __restrict__ db, int groups, int D, int K) {
@@ -311,14 +548,22 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((a.D + 127) / 128, chunks, a.B);
     const unsigned sb = static_cast<unsigned>((static_cast<long long>(a.B) * a.D + 127) / 128);
+    const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
+    const int vec = static_cast<int>(16 / es);
+    const bool use_vec = conv_vec_ok(a.K, a.D, vec, es, {a.x, a.u}, {a.ld_x, a.ld_u}) &&
+                         reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
+    dim3 vgrid((a.D / vec + 63) / 64, (a.T + kConvFwdTT - 1) / kConvFwdTT, a.B);
     if (a.dtype == MAMBA_B200_F32) {
-        conv1d_fwd_kernel<float><<<grid, 128, 0, st>>>(p);
+        if (use_vec) conv1d_fwd_vec_kernel<float><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_fwd_kernel<float><<<grid, 128, 0, st>>>(p);
         if (a.conv_state) conv1d_state_kernel<float><<<sb, 128, 0, st>>>(p);
     } else if (a.dtype == MAMBA_B200_F16) {
-        conv1d_fwd_kernel<__half><<<grid, 128, 0, st>>>(p);
+        if (use_vec) conv1d_fwd_vec_kernel<__half><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_fwd_kernel<__half><<<grid, 128, 0, st>>>(p);
         if (a.conv_state) conv1d_state_kernel<__half><<<sb, 128, 0, st>>>(p);
     } else {
-        conv1d_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+        if (use_vec) conv1d_fwd_vec_kernel<__nv_bfloat16><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
         if (a.conv_state) conv1d_state_kernel<__nv_bfloat16><<<sb, 128, 0, st>>>(p);
     }
     MB200_CUDA_CHECK(c, cudaGetLastError());
@@ -352,9 +597,20 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     p.B = a.B; p.T = a.T; p.D = a.D; p.K = a.K;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((a.D + 127) / 128, chunks, a.B);
-    if (a.dtype == MAMBA_B200_F32) conv1d_bwd_kernel<float><<<grid, 128, 0, st>>>(p);
-    else if (a.dtype == MAMBA_B200_F16) conv1d_bwd_kernel<__half><<<grid, 128, 0, st>>>(p);
-    else conv1d_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+    const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
+    const bool use_vec = conv_vec_ok(a.K, a.D, 4, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx}) &&
+                         reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
+    dim3 vgrid((a.D / 4 + 63) / 64, chunks, a.B);
+    if (a.dtype == MAMBA_B200_F32) {
+        if (use_vec) conv1d_bwd_vec_kernel<float><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_bwd_kernel<float><<<grid, 128, 0, st>>>(p);
+    } else if (a.dtype == MAMBA_B200_F16) {
+        if (use_vec) conv1d_bwd_vec_kernel<__half><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_bwd_kernel<__half><<<grid, 128, 0, st>>>(p);
+    } else {
+        if (use_vec) conv1d_bwd_vec_kernel<__nv_bfloat16><<<vgrid, 64, 0, st>>>(p);
+        else conv1d_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+    }
     MB200_CUDA_CHECK(c, cudaGetLastError());
     const int n = a.D * (a.K + 1);
     conv1d_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(p.part, a.dconv_w, a.dconv_b, a.B * chunks,

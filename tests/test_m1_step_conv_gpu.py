@@ -73,7 +73,7 @@ def test_prefill_then_decode_handoff(cuda_dev):
 
 @pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("shape", [(2, 1, 16, 4), (1, 3, 5, 4), (2, 64, 48, 4), (1, 65, 130, 4), (2, 200, 33, 3),
-                                   (1, 130, 8, 2), (1, 70, 12, 1), (1, 129, 20, 8)],
+                                   (1, 130, 8, 2), (1, 70, 12, 1), (1, 129, 20, 8), (1, 100, 1024, 4), (2, 40, 520, 3)],
                          ids=lambda s: "B%dT%dD%dK%d" % s)
 def test_conv1d_forward_and_backward_match_oracle(cuda_dev, shape, dt):
     import torch
