@@ -231,34 +231,48 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const ConvParams p) {
 
 // ---------------------------------------------------------------------------
 // Vector variants (d_conv <= 4, rows and pointers aligned to the vector): a
-// thread owns VEC adjacent channels and moves them with one 8- or 16-byte
-// access per step, four steps of loads in flight.  Same arithmetic, in the same
-// order per channel, as the scalar kernels above.
+// thread owns VEC adjacent channels and moves them with one 4- to 16-byte access
+// per step, kConvUnr steps of loads in flight.  Same arithmetic, in the same
+// order per channel, as the scalar kernels above.  The defaults (8-byte accesses
+// forward, 2 channels backward, 32-step forward chunks, 2 steps in flight) are the
+// fastest of the combinations timed at B 16, L 2048, D 1536, bf16: wider vectors
+// and deeper unrolling cost more in registers (occupancy) than they save.
 // ---------------------------------------------------------------------------
 constexpr int kConvKV = 4;     // widest d_conv of the vector kernels
-constexpr int kConvFwdTT = 64;  // timesteps per thread, forward
+#ifndef MB200_CONV_FWD_TT
+#define MB200_CONV_FWD_TT 32
+#endif
+#ifndef MB200_CONV_UNR
+#define MB200_CONV_UNR 2
+#endif
+#ifndef MB200_CONV_BWD_VEC
+#define MB200_CONV_BWD_VEC 2
+#endif
+#ifndef MB200_CONV_FWD_BYTES
+#define MB200_CONV_FWD_BYTES 8
+#endif
+constexpr int kConvFwdTT = MB200_CONV_FWD_TT;  // timesteps per thread, forward
+constexpr int kConvUnr = MB200_CONV_UNR;        // steps of loads in flight per thread
 
 template <typename Tact, int VEC>
 __device__ __forceinline__ void load_vec(const Tact* ptr, float* out) {
-    if (sizeof(Tact) * VEC == 16) {
+    constexpr int BYTES = sizeof(Tact) * VEC;
+    static_assert(BYTES == 16 || BYTES == 8 || BYTES == 4, "vector access of 4, 8 or 16 bytes");
+    uint32_t w[BYTES / 4];
+    if constexpr (BYTES == 16) {
         const uint4 v = *reinterpret_cast<const uint4*>(ptr);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        if (sizeof(Tact) == 4) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) out[i] = __uint_as_float(w[i]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const Tact* h = reinterpret_cast<const Tact*>(&w[i]);
-                out[2 * i] = to_f(h[0]);
-                out[2 * i + 1] = to_f(h[1]);
-            }
-        }
-    } else {  // 8 bytes: four 16-bit values
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else if constexpr (BYTES == 8) {
         const uint2 v = *reinterpret_cast<const uint2*>(ptr);
-        const uint32_t w[2] = {v.x, v.y};
+        w[0] = v.x; w[1] = v.y;
+    } else {
+        w[0] = *reinterpret_cast<const uint32_t*>(ptr);
+    }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < BYTES / 4; ++i) {
+        if (sizeof(Tact) == 4) {
+            out[i] = __uint_as_float(w[i]);
+        } else {
             const Tact* h = reinterpret_cast<const Tact*>(&w[i]);
             out[2 * i] = to_f(h[0]);
             out[2 * i + 1] = to_f(h[1]);
@@ -267,11 +281,13 @@ __device__ __forceinline__ void load_vec(const Tact* ptr, float* out) {
 }
 template <typename Tact, int VEC>
 __device__ __forceinline__ void store_vec(Tact* ptr, const float* v) {
+    constexpr int BYTES = sizeof(Tact) * VEC;
     __align__(16) Tact tmp[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) tmp[i] = from_f<Tact>(v[i]);
-    if (sizeof(Tact) * VEC == 16) *reinterpret_cast<uint4*>(ptr) = *reinterpret_cast<const uint4*>(tmp);
-    else *reinterpret_cast<uint2*>(ptr) = *reinterpret_cast<const uint2*>(tmp);
+    if (BYTES == 16) *reinterpret_cast<uint4*>(ptr) = *reinterpret_cast<const uint4*>(tmp);
+    else if (BYTES == 8) *reinterpret_cast<uint2*>(ptr) = *reinterpret_cast<const uint2*>(tmp);
+    else *reinterpret_cast<uint32_t*>(ptr) = *reinterpret_cast<const uint32_t*>(tmp);
 }
 
 // Taps of VEC adjacent channels, right-aligned in KV slots (absent taps zero), and bias.
@@ -279,10 +295,15 @@ template <int VEC>
 __device__ __forceinline__ void conv_load_taps(const ConvParams& p, int d, float (*w)[VEC], float* bias) {
     constexpr int KV = kConvKV;
     const int K = p.K;
+    if (VEC % 4 == 0) {
 #pragma unroll
-    for (int v = 0; v < VEC; v += 4) {
-        const float4 bv = *reinterpret_cast<const float4*>(p.bias + d + v);
-        bias[v] = bv.x; bias[v + 1] = bv.y; bias[v + 2] = bv.z; bias[v + 3] = bv.w;
+        for (int v = 0; v + 3 < VEC; v += 4) {
+            const float4 bv = *reinterpret_cast<const float4*>(p.bias + d + v);
+            bias[v] = bv.x; bias[v + 1] = bv.y; bias[v + 2] = bv.z; bias[v + 3] = bv.w;
+        }
+    } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) bias[v] = p.bias[d + v];
     }
     if (K == KV) {  // one 16-byte load per channel
 #pragma unroll
@@ -303,7 +324,7 @@ __device__ __forceinline__ void conv_load_taps(const ConvParams& p, int d, float
 
 template <typename Tact>
 __global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) {
-    constexpr int VEC = 16 / sizeof(Tact), KV = kConvKV;
+    constexpr int VEC = MB200_CONV_FWD_BYTES / sizeof(Tact), KV = kConvKV;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const int t0 = blockIdx.y * kConvFwdTT, b = blockIdx.z;
     if (d >= p.D) return;
@@ -325,14 +346,14 @@ __global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) 
                 win[k][v] = k - (KV - K) >= 0 ? conv_x_at(p, xb + v, b, d + v, t0 - (KV - 1) + k) : 0.0f;
     }
     const int t1 = min(p.T, t0 + kConvFwdTT);
-    for (int tb = t0; tb < t1; tb += 4) {
-        float cur[4][VEC];
+    for (int tb = t0; tb < t1; tb += kConvUnr) {
+        float cur[kConvUnr][VEC];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kConvUnr; ++i) {
             if (tb + i < t1) load_vec<Tact, VEC>(xb + static_cast<long long>(tb + i) * p.ld_x, cur[i]);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kConvUnr; ++i) {
             if (tb + i < t1) {
                 float o[VEC];
 #pragma unroll
@@ -354,7 +375,7 @@ __global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) 
 
 template <typename Tact>
 __global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) {
-    constexpr int VEC = 4, KV = kConvKV;
+    constexpr int VEC = (MB200_CONV_BWD_VEC == 8 && sizeof(Tact) == 2) ? 8 : (MB200_CONV_BWD_VEC == 2 && sizeof(Tact) == 2) ? 2 : 4, KV = kConvKV;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const int chunk = blockIdx.y, t0 = chunk * kConvTT, b = blockIdx.z;
     if (d >= p.D) return;
@@ -387,12 +408,12 @@ __global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) 
             if (k < KV - 1) dco[k][v] = 0.0f;
         }
     }
-    for (int tb = t_start; tb >= t0; tb -= 4) {
+    for (int tb = t_start; tb >= t0; tb -= kConvUnr) {
         // loads of four steps: d_u[t] and the input that enters the window when it
         // slides back past t (x[t - K], from the entering state when negative)
-        float g4[4][VEC], xin[4][VEC];
+        float g4[kConvUnr][VEC], xin[kConvUnr][VEC];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kConvUnr; ++i) {
             const int t = tb - i;
             if (t >= t0) {
                 load_vec<Tact, VEC>(gb + static_cast<long long>(t) * p.ld_du, g4[i]);
@@ -405,7 +426,7 @@ __global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) 
             }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kConvUnr; ++i) {
             const int t = tb - i;
             if (t >= t0) {
                 float dxv[VEC];
@@ -549,7 +570,7 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream,
     dim3 grid((a.D + 127) / 128, chunks, a.B);
     const unsigned sb = static_cast<unsigned>((static_cast<long long>(a.B) * a.D + 127) / 128);
     const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
-    const int vec = static_cast<int>(16 / es);
+    const int vec = static_cast<int>(MB200_CONV_FWD_BYTES / es);
     const bool use_vec = conv_vec_ok(a.K, a.D, vec, es, {a.x, a.u}, {a.ld_x, a.ld_u}) &&
                          reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
     dim3 vgrid((a.D / vec + 63) / 64, (a.T + kConvFwdTT - 1) / kConvFwdTT, a.B);
@@ -598,9 +619,10 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((a.D + 127) / 128, chunks, a.B);
     const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
-    const bool use_vec = conv_vec_ok(a.K, a.D, 4, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx}) &&
+    const int bvec = (MB200_CONV_BWD_VEC == 8 && es == 2) ? 8 : (MB200_CONV_BWD_VEC == 2 && es == 2) ? 2 : 4;
+    const bool use_vec = conv_vec_ok(a.K, a.D, bvec, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx}) &&
                          reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
-    dim3 vgrid((a.D / 4 + 63) / 64, chunks, a.B);
+    dim3 vgrid((a.D / bvec + 63) / 64, chunks, a.B);
     if (a.dtype == MAMBA_B200_F32) {
         if (use_vec) conv1d_bwd_vec_kernel<float><<<vgrid, 64, 0, st>>>(p);
         else conv1d_bwd_kernel<float><<<grid, 128, 0, st>>>(p);

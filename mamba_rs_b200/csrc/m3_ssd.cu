@@ -123,8 +123,8 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // that holds w o V for the state update and then the 16-bit copy of the new
 // state for the next chunk's Y2; then f32 vectors, barriers.
 constexpr uint32_t kQ = 0, kM = 0, kK = 32768, kV = 65536, kVw = 81920, kS = 81920;
-constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128]
-constexpr uint32_t kBar = kVec + 3 * 128 * 4, kTmemSlot = kBar + 16;
+constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128]
+constexpr uint32_t kBar = kVec + 4 * 128 * 4, kTmemSlot = kBar + 16;
 constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
 constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
@@ -137,7 +137,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 }
 
 template <typename Th>
-__global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
+__global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // two threads per step: thread (row, half) owns row `row` of the chunk (TMEM lane
     // `row`) and half of that row's columns in every elementwise stage
@@ -181,20 +181,24 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
     const int r8 = lane & 7, jc = lane >> 3;
     auto issue_qk = [&](const Th* src, uint32_t tile, int c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
+        const Th* base = src + ((static_cast<long long>(b) * T + t0) * nh + h) * NS + 8 * jc;
+        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const int task = i * 8 + wfull, row = (task >> 2) * 8 + r8, j = (task & 3) * 4 + jc;
-            cp_async16(smem + tile + chunk_off(row, j, NS),
-                       src + ((static_cast<long long>(b) * T + t0 + min(row, nv - 1)) * nh + h) * NS + 8 * j, row < nv);
+            const int task = i * 8 + wfull, rg = task >> 2, jg = task & 3, row = rg * 8 + r8;
+            cp_async16(smem + dst0 + rg * 2048 + jg * 512,
+                       base + static_cast<long long>(min(row, nv - 1)) * nh * NS + 32 * jg, row < nv);
         }
     };
     auto issue_v = [&](uint32_t tile, int c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
+        const Th* base = xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD + 8 * jc;
+        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int task = i * 8 + wfull, row = (task >> 1) * 8 + r8, j = (task & 1) * 4 + jc;
-            cp_async16(smem + tile + chunk_off(row, j, HD),
-                       xg + (static_cast<long long>(b) * T + t0 + min(row, nv - 1)) * nh * HD + h * HD + 8 * j, row < nv);
+            const int task = i * 8 + wfull, rg = task >> 1, jg = task & 1, row = rg * 8 + r8;
+            cp_async16(smem + dst0 + rg * 1024 + jg * 512,
+                       base + static_cast<long long>(min(row, nv - 1)) * nh * HD + 32 * jg, row < nv);
         }
     };
     // Per-row scalars of chunk c into stage `st`: inclusive cumsum of adt, scale, gamma.
@@ -225,6 +229,7 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
         for (int w = 0; w < warp; ++w) off += dA[w];
         __syncthreads();
         dA[tid] = run + off;
+        dA[384 + tid] = (run + off) * kLog2e;
         __syncthreads();
     };
 
@@ -279,34 +284,50 @@ __global__ void __launch_bounds__(256) m3_ssd_fwd_tc_kernel(const M3Params p) {
                     *reinterpret_cast<uint4*>(smem + kVw + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
             }
-            const float dAt = dA[tid], gt = gam[tid];
-            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
-                if (q4 > warp) {  // wholly above the diagonal for every row of this warp
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) = make_uint4(0, 0, 0, 0);
-                    continue;
-                }
+            const float* dAl = dA + 384;  // dA * log2(e)
+            const float dAlt = dAl[tid], gt = gam[tid];
+            // One 32-column block of row `tid`.  Blocks left of the diagonal block need no
+            // mask; rows and columns past the end of the sequence need none either (their
+            // V rows are zero and their y rows are never stored).
+            auto mask_block = [&](auto diag_tag, int q4) {
+                constexpr bool DIAG = decltype(diag_tag)::value;
                 float g[32];
                 tmem_ld32(lane_addr + cG + q4 * 32, g);
                 uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float m2[2];
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 da4 = *reinterpret_cast<const float4*>(dAl + q4 * 32 + i);
+                    const float4 sc4 = *reinterpret_cast<const float4*>(scl + q4 * 32 + i);
+                    const float dav[4] = {da4.x, da4.y, da4.z, da4.w}, scv[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+                    float m[4];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int s = q4 * 32 + i + u;
-                        float m = 0.0f;
-                        if (s < tid) m = g[i + u] * scl[s] * ex2((dAt - dA[s]) * kLog2e);
-                        else if (s == tid) m = fmaf(g[i + u], gt, Dv);
-                        m2[u] = (row_ok && s < nv) ? m : 0.0f;
+                    for (int u = 0; u < 4; ++u) {
+                        float v = g[i + u] * scv[u] * ex2(dAlt - dav[u]);
+                        if (DIAG) {
+                            const int s = q4 * 32 + i + u;
+                            if (s > tid) v = 0.0f;
+                            else if (s == tid) v = fmaf(g[i + u], gt, Dv);
+                        }
+                        m[u] = v;
                     }
-                    packed[i / 2] = pack2<Th>(m2[0], m2[1]);
+                    packed[i / 2] = pack2<Th>(m[0], m[1]);
+                    packed[i / 2 + 1] = pack2<Th>(m[2], m[3]);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) =
                         make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            };
+            for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
+                if (q4 > warp) {  // wholly above the diagonal for every row of this warp
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) = make_uint4(0, 0, 0, 0);
+                } else if (q4 == warp) {
+                    mask_block(std::true_type{}, q4);
+                } else {
+                    mask_block(std::false_type{}, q4);
+                }
             }
             if (c > 0) {  // S^T row `tid` (state index n = tid) *= exp(dA_end)
                 const float e_end = ex2(dA[nv - 1] * kLog2e);
