@@ -323,8 +323,8 @@ using namespace tc;
 constexpr int CS = 128, HD = 64, NS = 128;
 constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kDS = 114688, kM1 = 131072,
                    kM2 = 163840, kEdY = 196608, kVec = 212992;
-// f32 vectors: dA, scl, gam, red (scratch), gdv, pdv, part[5]
-constexpr uint32_t kBar = kVec + 11 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
+// f32 vectors: dA, scl, gam, red (scratch), gdv, pdv, part[5], dA*log2(e)
+constexpr uint32_t kBar = kVec + 12 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
 constexpr uint32_t c0 = 0, c1 = 128, c2 = 256, c3 = 384, cDS = 448, kTmemCols = 512;
 constexpr uint32_t kStateTile = NS * HD * 2;  // bytes of one 16-bit state copy
 
@@ -343,6 +343,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     float* gdv = dA + 512;
     float* pdv = dA + 640;
     float* part = dA + 768;  // [5][128]: partial sums of the upper-half threads
+    float* dAl = dA + 1408;  // dA * log2(e)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
     const uint32_t sbase = smem_u32(smem);
@@ -401,6 +402,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         for (int w = 0; w < warp; ++w) off += red[w];
         run += off;
         dA[tid] = run;
+        dAl[tid] = run * kLog2e;
         __syncthreads();
         run_o = run; g_o = g; s_o = s;
     };
@@ -564,40 +566,41 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         wait_bar(0);
         // ---- epilogue 1 ----
         float rowX = 0.0f, gd = 0.0f, pd = 0.0f, qr = 0.0f, ds_part = 0.0f;
-        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
-            if (q4 > warp) {  // wholly above the diagonal for every row of this warp
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
-                    *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
-                }
-                continue;
-            }
+        // One 32-column block of row `tid` of M1 = scale L o P and M2 = scale L o G.  Blocks
+        // left of the diagonal block need no mask; rows and columns past the end of the
+        // sequence come out as exact zeros (their Q, dY rows and scale are zero).
+        const float dAl_t = dAl[tid];
+        auto mask_block = [&](auto diag_tag, int q4) {
+            constexpr bool DIAG = decltype(diag_tag)::value;
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
             uint32_t pk1[16], pk2[16];
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float m1[2], m2[2];
+            for (int i = 0; i < 32; i += 4) {
+                const float4 da4 = *reinterpret_cast<const float4*>(dAl + q4 * 32 + i);
+                const float4 sc4 = *reinterpret_cast<const float4*>(scl + q4 * 32 + i);
+                const float dav[4] = {da4.x, da4.y, da4.z, da4.w}, scv[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+                float m1[4], m2[4];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int s = q4 * 32 + i + u;
-                    float a1 = 0.0f, a2v = 0.0f;
-                    if (s < tid && row_ok) {
-                        const float f = scl[s] * ex2((dA_t - dA[s]) * kLog2e);
-                        a1 = f * pv[i + u];
-                        a2v = f * gv[i + u];
-                        rowX = fmaf(a1, gv[i + u], rowX);
-                    } else if (s == tid) {
-                        gd = gv[i + u];
-                        pd = pv[i + u];
+                for (int u = 0; u < 4; ++u) {
+                    float f = scv[u] * ex2(dAl_t - dav[u]);
+                    if (DIAG) {
+                        const int s = q4 * 32 + i + u;
+                        if (s >= tid) f = 0.0f;
+                        if (s == tid) {
+                            gd = gv[i + u];
+                            pd = pv[i + u];
+                        }
                     }
-                    m1[u] = a1;
-                    m2[u] = a2v;
+                    m1[u] = f * pv[i + u];
+                    m2[u] = f * gv[i + u];
+                    rowX = fmaf(m1[u], gv[i + u], rowX);
                 }
                 pk1[i / 2] = pack2<Th>(m1[0], m1[1]);
+                pk1[i / 2 + 1] = pack2<Th>(m1[2], m1[3]);
                 pk2[i / 2] = pack2<Th>(m2[0], m2[1]);
+                pk2[i / 2 + 1] = pack2<Th>(m2[2], m2[3]);
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -605,6 +608,19 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                     make_uint4(pk1[4 * j], pk1[4 * j + 1], pk1[4 * j + 2], pk1[4 * j + 3]);
                 *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) =
                     make_uint4(pk2[4 * j], pk2[4 * j + 1], pk2[4 * j + 2], pk2[4 * j + 3]);
+            }
+        };
+        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
+            if (q4 > warp) {  // wholly above the diagonal for every row of this warp
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
+                }
+            } else if (q4 == warp) {
+                mask_block(std::true_type{}, q4);
+            } else {
+                mask_block(std::false_type{}, q4);
             }
         }
         if ((tid >> 6) == half) {  // the diagonal lies in this thread's columns
@@ -683,16 +699,26 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         gd = gdv[tid];
         pd = pdv[tid];
         float dsc = 0.0f;
-        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
-            if (q4 < warp) continue;  // only later steps (tt > s) contribute
+        auto colsum_block = [&](auto diag_tag, int q4) {
+            constexpr bool DIAG = decltype(diag_tag)::value;
             float gv[32], pv[32];
             tmem_ld32(lane_addr + c0 + q4 * 32, gv);
             tmem_ld32(lane_addr + c1 + q4 * 32, pv);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int tt = q4 * 32 + i;
-                if (tt > tid && tt < nv) dsc = fmaf(ex2((dA[tt] - dA_t) * kLog2e) * gv[i], pv[i], dsc);
+            for (int i = 0; i < 32; i += 4) {
+                const float4 da4 = *reinterpret_cast<const float4*>(dAl + q4 * 32 + i);
+                const float dav[4] = {da4.x, da4.y, da4.z, da4.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float f = ex2(dav[u] - dAl_t);
+                    if (DIAG && q4 * 32 + i + u <= tid) f = 0.0f;
+                    dsc = fmaf(f * gv[i + u], pv[i + u], dsc);
+                }
             }
+        };
+        for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {  // only later steps (tt > s) contribute
+            if (q4 == warp) colsum_block(std::true_type{}, q4);
+            else if (q4 > warp) colsum_block(std::false_type{}, q4);
         }
         {
             const float gp = g_t * pd;  // gamma_t P_tt
