@@ -129,13 +129,6 @@ constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
 constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
 
-// 16-byte asynchronous copy global -> shared; `valid` false writes zeros.
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
-                 "r"(valid ? 16u : 0u)
-                 : "memory");
-}
-
 template <typename Th>
 __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];

@@ -421,6 +421,19 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         return red[0] + red[1] + red[2] + red[3];
     };
 
+    // Cooperative asynchronous load of a [128 x C] tile of 16-bit rows (row stride `ld`
+    // elements) into the core-matrix layout; rows >= nv are zero-filled.
+    const int r8 = threadIdx.x & 7, jc = (threadIdx.x & 31) >> 3, wfull = threadIdx.x >> 5;
+    auto issue_rows = [&](const Th* base, long long ld, uint32_t tile, int C, int nv) {
+        const int jgroups = C / 32;  // groups of four 16-byte pieces per row
+        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
+        for (int task = wfull; task < 16 * jgroups; task += 8) {
+            const int rg = task / jgroups, jg = task - rg * jgroups, row = rg * 8 + r8;
+            cp_async16(smem + dst0 + rg * (C / 8) * 128 + jg * 512,
+                       base + static_cast<long long>(min(row, nv - 1)) * ld + 8 * jc + 32 * jg, row < nv);
+        }
+    };
+
     // ---------------- A. forward: 16-bit copies of the entering states ----------------
     for (int c = 0; c < nc; ++c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
@@ -496,6 +509,18 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const int t = t0 + tid;
         const bool row_ok = tid < nv;
         const bool has_sin = c > 0;
+        // ---- loads (asynchronous, 8 rows x 64 bytes per warp instruction) under the scalars ----
+        issue_rows(Qg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kQ, NS, nv);
+        issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kK, NS, nv);
+        issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kV, HD, nv);
+        issue_rows(dyg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kDY, HD, nv);
+        if (has_sin) {
+            const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                cp_async16(smem + kSin + (j * 256 + threadIdx.x) * 16, src + j * 256 + threadIdx.x, true);
+        }
+        cp_async_commit();
         float run, g_t, s_t;
         load_scalars(t0, nv, run, g_t, s_t);
         const float dA_t = run, dA_end = dA[nv - 1];
@@ -504,26 +529,12 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const float w_t = lend_t * s_t;
         const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
         const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
-        // ---- loads: rows of Q, K, V, dY, E o dY; the entering state's tile ----
-#pragma unroll
-        for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
-            uint4 q = zero4, k = zero4;
-            if (row_ok) {
-                q = *reinterpret_cast<const uint4*>(Qg + qk_row + 8 * j);
-                k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
-            }
-            *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = q;
-            *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
-        }
+        cp_async_wait_all();
+        __syncthreads();
+        // E o dY from the landed dY tile (own row, own half of the columns)
 #pragma unroll
         for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-            uint4 v = zero4, dyv = zero4;
-            if (row_ok) {
-                v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
-                dyv = *reinterpret_cast<const uint4*>(dyg + x_row + 8 * j);
-            }
-            *reinterpret_cast<uint4*>(smem + kV + chunk_off(tid, j, HD)) = v;
-            *reinterpret_cast<uint4*>(smem + kDY + chunk_off(tid, j, HD)) = dyv;
+            const uint4 dyv = *reinterpret_cast<const uint4*>(smem + kDY + chunk_off(tid, j, HD));
             uint32_t w4[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
@@ -531,12 +542,6 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                 w4[q4] = pack2<Th>(f.x * e_t, f.y * e_t);
             }
             *reinterpret_cast<uint4*>(smem + kEdY + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-        }
-        if (has_sin) {
-            const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
-#pragma unroll
-            for (int j = half * 4; j < half * 4 + 4; ++j)
-                *reinterpret_cast<uint4*>(smem + kSin + (j * 128 + tid) * 16) = src[j * 128 + tid];
         }
         fence_proxy_async();
         fence_before();

@@ -102,6 +102,15 @@ __device__ __forceinline__ uint32_t chunk_off(int r, int j, int C) {
 }
 
 
+// 16-byte asynchronous copy global -> shared; `valid` false writes zeros.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(valid ? 16u : 0u)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // Descriptors of the k-th 16-element step of a tile with C columns (see top).
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int k, int C) {
     return smem_desc(tile + k * 256, 128, (C >> 3) * 128);
