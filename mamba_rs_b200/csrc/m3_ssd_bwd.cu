@@ -440,22 +440,17 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const bool last = c + 1 == nc;
         float run = 0.0f, g = 0.0f, s = 0.0f;
         if (!last) {
+            issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kK, NS, nv);
+            issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kV, HD, nv);
+            cp_async_commit();
             load_scalars(t0, nv, run, g, s);
             const float dA_end = dA[nv - 1];
             const float wt = tid < nv ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
-            const int t = t0 + tid;
-            const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
-            const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
-#pragma unroll
-            for (int j = half * (NS / 16); j < (half + 1) * (NS / 16); ++j) {
-                uint4 k = zero4;
-                if (tid < nv) k = *reinterpret_cast<const uint4*>(Kg + qk_row + 8 * j);
-                *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = k;
-            }
+            cp_async_wait_all();
+            __syncthreads();
 #pragma unroll
             for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                uint4 v = zero4;
-                if (tid < nv) v = *reinterpret_cast<const uint4*>(xg + x_row + 8 * j);
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + kV + chunk_off(tid, j, HD));
                 uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
