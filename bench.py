@@ -19,6 +19,8 @@ path.  Rank 0 prints one JSON line.
             the launching stream) against the measured HBM copy peak
   cpu_baseline: the CPU restatement of the reference's CPU path timed on the
             host cores of this box on a bounded sample of the same workload
+  backward: (1 GPU) the fused BPTT backward of the same workload, timed after
+            the headline region: ms, algorithmic GB/s, fraction of the HBM peak
 
 --impl reference times that CPU path alone (the reference is Rust and cannot
 be built without cargo; its CPU algorithm is restated in oracle/).
@@ -303,6 +305,32 @@ def main():
         e2e_ms = f0.elapsed_time(f1) / n_e2e
     clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions
 
+    # ---- the training pair of the same workload (reported beside the headline, not part of it) ----
+    bwd = None
+    if rank == 0 and world == 1 and not args.no_e2e:
+        S = 32
+        cs = torch.empty(B, (T + S - 1) // S, D, N, device=dev)
+        dy = torch.randn(B, T, D, device=dev).to(td)
+        ws = torch.empty(mb.selective_scan_bwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=dev)
+        mb.selective_scan_fwd(devt["x"], devt["delta_raw"], devt["Bm"], devt["Cm"], a_neg, Dp, devt["z"],
+                              chunk_states=cs, save_stride=S, y=y, handle=handle)
+        run_bwd = lambda: mb.selective_scan_bwd(devt["x"], devt["delta_raw"], devt["Bm"], devt["Cm"], a_neg, Dp,
+                                                dy, cs, S, devt["z"], workspace=ws, handle=handle)
+        for _ in range(3):
+            run_bwd()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(10):
+            run_bwd()
+        g1.record()
+        torch.cuda.synchronize()
+        bms = g0.elapsed_time(g1) / 10
+        bby = 7 * 2 * B * T * D + 2 * 2 * B * T * N + 2 * 4 * B * T * N + 4 * B * ((T + S - 1) // S) * D * N
+        bwd = {"ms": bms, "algorithmic_bytes": bby, "GBps": bby / (bms * 1e-3) / 1e9, "save_stride": S,
+               "kernels_per_call": 3}
+        del cs, dy, ws
+
     times = torch.tensor([total_ms, 0.0 if args.no_e2e else e2e_ms, kern_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -335,6 +363,9 @@ def main():
                          "kernel": "sscan_fwd_kernel", "kernel_ms": kern_ms,
                          "algorithmic_bytes": by},
         }
+        if bwd is not None:
+            bwd["frac_of_hbm_peak"] = bwd["GBps"] / peak
+            out["backward"] = bwd
         if world == 1 and not args.no_cpu_baseline:
             val, cores, secs = cpu_leg(sample_B=B, sample_D=D)
             out["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",

@@ -598,8 +598,10 @@ static int build_fwd_variants(FwdVariant* v) {
     v[n++] = make_variant<Tact, 4, 1>();
     v[n++] = make_variant<Tact, 8, 1>();
 #endif
-#ifdef MB200_FWD_NS16
+#if defined(MB200_FWD_NS16)
     v[n++] = make_variant<Tact, 16, 1>();
+#elif defined(MB200_FWD_NS4)
+    v[n++] = make_variant<Tact, 4, 4>();
 #else
     v[n++] = make_variant<Tact, 8, 2>();
 #endif

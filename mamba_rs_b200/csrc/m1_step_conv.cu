@@ -485,16 +485,40 @@ static bool conv_vec_ok(int K, int D, int vec, size_t esize, std::initializer_li
     return true;
 }
 
-// dW[D,K] += sum over (b, chunk) partials; db[D] likewise, in index order.
-__global__ void conv1d_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dW,
-                                         float* __restrict__ db, int groups, int D, int K) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= D * (K + 1)) return;
+// dW[D,K] += sum over (b, chunk) partials; db[D] likewise.  A block owns 32
+// consecutive outputs; warp w adds the groups g = w, w+8, ... (coalesced
+// 128-byte rows, several loads in flight) and the eight warp sums are added
+// in warp order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) conv1d_bwd_reduce_kernel(const float* __restrict__ part,
+                                                                float* __restrict__ dW, float* __restrict__ db,
+                                                                int groups, int D, int K) {
+    __shared__ float sums[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + lane, n = D * (K + 1);
     float acc = 0.0f;
-    for (int g = 0; g < groups; ++g) acc += part[static_cast<long long>(g) * D * (K + 1) + i];
-    const int d = i / (K + 1), k = i % (K + 1);
-    if (k < K) dW[d * K + k] += acc;
-    else db[d] += acc;
+    if (i < n) {
+        const long long stride = static_cast<long long>(n);
+        int g = w;
+        for (; g + 24 < groups; g += 32) {
+            const float a0 = part[g * stride + i], a1 = part[(g + 8) * stride + i];
+            const float a2 = part[(g + 16) * stride + i], a3 = part[(g + 24) * stride + i];
+            acc += a0;
+            acc += a1;
+            acc += a2;
+            acc += a3;
+        }
+        for (; g < groups; g += 8) acc += part[g * stride + i];
+    }
+    sums[w][lane] = acc;
+    __syncthreads();
+    if (w == 0 && i < n) {
+        float t = sums[0][lane];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) t += sums[k][lane];
+        const int d = i / (K + 1), kk = i % (K + 1);
+        if (kk < K) dW[d * K + kk] += t;
+        else db[d] += t;
+    }
 }
 
 }  // namespace mb200
@@ -635,7 +659,7 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     }
     MB200_CUDA_CHECK(c, cudaGetLastError());
     const int n = a.D * (a.K + 1);
-    conv1d_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(p.part, a.dconv_w, a.dconv_b, a.B * chunks,
+    conv1d_bwd_reduce_kernel<<<(n + 31) / 32, 256, 0, st>>>(p.part, a.dconv_w, a.dconv_b, a.B * chunks,
                                                              a.D, a.K);
     MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;
