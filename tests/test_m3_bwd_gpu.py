@@ -105,3 +105,37 @@ def test_backward_validation(cuda_dev):
     tb = {k: to_dev(v, cuda_dev) for k, v in big.items() if k in ARGS}
     with pytest.raises(RuntimeError, match="headdim"):
         mb.m3_ssd_bwd(*[tb[k] for k in ARGS], torch.zeros_like(tb["x"]))
+
+
+def test_tensor_core_backward_is_linear_in_dy_at_config4_size(cuda_dev):
+    """Benchmark geometry (B 8, L 4096, 32 heads x 64, d_state 128, bf16):
+    bwd(dy1 + dy2) = bwd(dy1) + bwd(dy2), every output, on the tcgen05 path."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, T, nh, hd, N = 8, 4096, 32, 64, 128
+    g = torch.Generator(device="cpu").manual_seed(6)
+    bf = torch.bfloat16
+    dev = cuda_dev
+    x = torch.randn(B, T, nh * hd, generator=g).to(dev).to(bf)
+    dy1 = torch.randn(B, T, nh * hd, generator=g).to(dev).to(bf)
+    dy2 = torch.randn(B, T, nh * hd, generator=g).to(dev).to(bf)
+    K = (torch.randn(B, T, nh, N, generator=g) * N ** -0.25).to(dev).to(bf)
+    Q = (torch.randn(B, T, nh, N, generator=g) * N ** -0.25).to(dev).to(bf)
+    A = -torch.exp(torch.rand(nh, generator=g) * np.log(16.0))
+    dt = torch.nn.functional.softplus(0.5 * torch.randn(B, T, nh, generator=g) - 4.0)
+    trap = torch.sigmoid(torch.randn(B, T, nh, generator=g))
+    adt = (A * dt).to(dev).contiguous()
+    dt, trap = dt.to(dev).contiguous(), trap.to(dev).contiguous()
+    Dh = torch.ones(nh, device=dev)
+    ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes(B, T, nh, hd, N), dtype=torch.uint8,
+                     device=dev)
+    run = lambda dy: mb.m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy, workspace=ws)
+    g1, g2 = run(dy1), run(dy2)
+    g12 = run((dy1.float() + dy2.float()).to(bf))
+    torch.cuda.synchronize()
+    mb.ffi.default_handle(0).check_status()
+    for k in ("dx", "dK", "dQ", "d_adt", "d_dt", "d_trap", "dD"):
+        want = g1[k].float() + g2[k].float()
+        err = float((g12[k].float() - want).abs().max() / want.abs().max())
+        assert err <= TOL["bf16"], (k, err)

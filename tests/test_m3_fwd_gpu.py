@@ -95,3 +95,41 @@ def test_tensor_core_and_sequential_kernels_agree(cuda_dev):
     y2, s2, _, _ = run_gpu(i, "bf16", cuda_dev, force_sequential=True)
     assert rel_err(y1, y2) <= TOL["bf16"]
     assert rel_err(s1, s2) <= TOL["bf16"]
+
+
+def test_tensor_core_kernel_at_config4_size_agrees_with_sequential_and_is_linear_in_x(cuda_dev):
+    """Benchmark geometry (B 8, L 4096, 32 heads x 64, d_state 128, bf16): the
+    tcgen05 kernel against the sequential kernel on the same device tensors, and
+    the size-independent property y(x1 + x2) = y(x1) + y(x2) - y(0) with y(0) = 0."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, T, nh, hd, N = 8, 4096, 32, 64, 128
+    g = torch.Generator(device="cpu").manual_seed(4)
+    bf = torch.bfloat16
+    dev = cuda_dev
+    x1 = torch.randn(B, T, nh * hd, generator=g).to(dev).to(bf)
+    x2 = torch.randn(B, T, nh * hd, generator=g).to(dev).to(bf)
+    K = (torch.randn(B, T, nh, N, generator=g) * N ** -0.25).to(dev).to(bf)
+    Q = (torch.randn(B, T, nh, N, generator=g) * N ** -0.25).to(dev).to(bf)
+    A = -torch.exp(torch.rand(nh, generator=g) * np.log(16.0))
+    dt = torch.nn.functional.softplus(0.5 * torch.randn(B, T, nh, generator=g) - 4.0)
+    trap = torch.sigmoid(torch.randn(B, T, nh, generator=g))
+    adt = (A * dt).to(dev).contiguous()
+    dt, trap = dt.to(dev).contiguous(), trap.to(dev).contiguous()
+    Dh = torch.ones(nh, device=dev)
+    s_tc = torch.zeros(B, nh, hd, N, device=dev)
+    s_seq = torch.zeros(B, nh, hd, N, device=dev)
+    y_tc = mb.m3_ssd_fwd(x1, K, Q, dt, trap, adt, Dh, ssm_state=s_tc).float()
+    y_seq = mb.m3_ssd_fwd(x1, K, Q, dt, trap, adt, Dh, ssm_state=s_seq, force_sequential=True).float()
+    torch.cuda.synchronize()
+    mb.ffi.default_handle(0).check_status()
+    den = y_seq.abs().max()
+    assert float((y_tc - y_seq).abs().max() / den) <= TOL["bf16"]
+    assert float((s_tc - s_seq).abs().max() / s_seq.abs().max()) <= TOL["bf16"]
+    del y_seq
+    x12 = (x1.float() + x2.float()).to(bf)  # rounding of the sum stays inside the tolerance
+    y2 = mb.m3_ssd_fwd(x2, K, Q, dt, trap, adt, Dh).float()
+    y12 = mb.m3_ssd_fwd(x12, K, Q, dt, trap, adt, Dh).float()
+    torch.cuda.synchronize()
+    assert float((y12 - (y_tc + y2)).abs().max() / y12.abs().max()) <= TOL["bf16"]
