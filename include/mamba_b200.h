@@ -318,7 +318,12 @@ typedef struct mamba_b200_m3_ssd_bwd_args {
     long long workspace_bytes; /* >= mamba_b200_m3_ssd_bwd_workspace_bytes(...) */
 } mamba_b200_m3_ssd_bwd_args;
 
+/* Upper bound over every dtype (the f32 CUDA-core kernel parks f32 states every 32
+ * steps); _for(dtype, ...) is what a call with that storage dtype needs when its
+ * tensors are 16-byte aligned: far less for the tensor-core geometry (16-bit, hd 64,
+ * N 128: 16-bit state tiles every 128 steps). */
 MAMBA_B200_API long long mamba_b200_m3_ssd_bwd_workspace_bytes(int B, int T, int nh, int hd, int N);
+MAMBA_B200_API long long mamba_b200_m3_ssd_bwd_workspace_bytes_for(int dtype, int B, int T, int nh, int hd, int N);
 MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream, const mamba_b200_m3_ssd_bwd_args* args);
 
 /*

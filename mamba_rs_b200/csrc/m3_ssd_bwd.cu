@@ -891,10 +891,19 @@ static size_t m3_bwd_smem(int hd, int N) {
     return sizeof(float) * (3 * kM3C * LQ + 3 * kM3C * LV + 2 * kM3C * LG + 2 * hd * LQ + 12 * 32);
 }
 
-static void m3_bwd_ws(int B, int T, int nh, int hd, int N, size_t* o_g, size_t* o_s, size_t* o_d, size_t* total) {
+// Tensor-core geometry: 16-bit storage, headdim 64, d_state 128.
+static bool m3_bwd_tc_shape(int dtype, int hd, int N) {
+    return dtype != MAMBA_B200_F32 && hd == tcb::HD && N == tcb::NS;
+}
+
+// States first (f32 every 32 steps for the CUDA-core kernel; 16-bit tiles every 128
+// steps for the tensor-core kernel), then dgamma, dscale [B,T,nh] and dD partials.
+static void m3_bwd_ws(bool tc, int B, int T, int nh, int hd, int N, size_t* o_g, size_t* o_s, size_t* o_d,
+                      size_t* total) {
     const size_t nc = (T + kM3C - 1) / kM3C;
     auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
-    const size_t st = al(sizeof(float) * static_cast<size_t>(B) * nh * nc * hd * N);
+    const size_t st = tc ? al(static_cast<size_t>(B) * nh * ((T + tcb::CS - 1) / tcb::CS) * tcb::kStateTile)
+                         : al(sizeof(float) * static_cast<size_t>(B) * nh * nc * hd * N);
     const size_t v = al(sizeof(float) * static_cast<size_t>(B) * T * nh);
     *o_g = st; *o_s = st + v; *o_d = st + 2 * v;
     *total = st + 2 * v + al(sizeof(float) * static_cast<size_t>(B) * nh);
@@ -922,7 +931,15 @@ using namespace mb200;
 extern "C" MAMBA_B200_API long long mamba_b200_m3_ssd_bwd_workspace_bytes(int B, int T, int nh, int hd, int N) {
     if (B <= 0 || T <= 0 || nh <= 0 || hd <= 0 || N <= 0) return 0;
     size_t a, b2, d, total;
-    m3_bwd_ws(B, T, nh, hd, N, &a, &b2, &d, &total);
+    m3_bwd_ws(false, B, T, nh, hd, N, &a, &b2, &d, &total);
+    return static_cast<long long>(total);
+}
+
+extern "C" MAMBA_B200_API long long mamba_b200_m3_ssd_bwd_workspace_bytes_for(int dtype, int B, int T, int nh,
+                                                                              int hd, int N) {
+    if (B <= 0 || T <= 0 || nh <= 0 || hd <= 0 || N <= 0) return 0;
+    size_t a, b2, d, total;
+    m3_bwd_ws(m3_bwd_tc_shape(dtype, hd, N), B, T, nh, hd, N, &a, &b2, &d, &total);
     return static_cast<long long>(total);
 }
 
@@ -942,8 +959,13 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     if (!a.x || !a.K || !a.Q || !a.dt || !a.trap || !a.adt || !a.Dh || !a.dy || !a.dx || !a.dK || !a.dQ ||
         !a.d_adt || !a.d_dt || !a.d_trap || !a.dD || !a.workspace)
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: null required pointer");
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    static const bool cuda_cores_env = getenv("MAMBA_B200_M3_BWD_CUDA_CORES") != nullptr;
+    const bool tensor_core = m3_bwd_tc_shape(a.dtype, a.hd, a.N) && !cuda_cores_env && al16(a.x) && al16(a.K) &&
+                             al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) && al16(a.dQ);
     size_t o_g, o_s, o_d, total;
-    m3_bwd_ws(a.B, a.T, a.nh, a.hd, a.N, &o_g, &o_s, &o_d, &total);
+    // a misaligned tensor-core-shaped call falls back to the CUDA-core kernel and its larger scratch
+    m3_bwd_ws(tensor_core, a.B, a.T, a.nh, a.hd, a.N, &o_g, &o_s, &o_d, &total);
     if (a.workspace_bytes < static_cast<long long>(total))
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: workspace %lld < %zu bytes", a.workspace_bytes, total);
     if (reinterpret_cast<uintptr_t>(a.workspace) % 256)
@@ -962,11 +984,6 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(a.nh, a.B);
     const size_t smem = m3_bwd_smem(a.hd, a.N);
-    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    static const bool cuda_cores_env = getenv("MAMBA_B200_M3_BWD_CUDA_CORES") != nullptr;
-    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd == tcb::HD && a.N == tcb::NS && !cuda_cores_env &&
-                             al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) &&
-                             al16(a.dQ);
     if (tensor_core) {
         if (a.dtype == MAMBA_B200_F16) tcb::m3_ssd_bwd_tc_kernel<__half><<<grid, 256, tcb::kSmem, st>>>(p);
         else tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16><<<grid, 256, tcb::kSmem, st>>>(p);

@@ -144,6 +144,7 @@ def lib() -> C.CDLL:
         bind("mamba_b200_m3_ssd_fwd", [vp, vp, C.POINTER(M3SsdArgs)])
         bind("mamba_b200_m3_ssd_bwd", [vp, vp, C.POINTER(M3SsdBwdArgs)])
         bind("mamba_b200_m3_ssd_bwd_workspace_bytes", [C.c_int] * 5, C.c_longlong)
+        bind("mamba_b200_m3_ssd_bwd_workspace_bytes_for", [C.c_int] * 6, C.c_longlong)
     return _lib
 
 

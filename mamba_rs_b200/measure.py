@@ -69,7 +69,7 @@ def main():
             fn = lambda: mb.m3_ssd_fwd(*a, ssm_state=ssm, y=y)
         else:
             dy = torch.randn(B, T, nh * hd, device=dev).to(bf)
-            ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes(B, T, nh, hd, N),
+            ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes_for(2, B, T, nh, hd, N),
                              dtype=torch.uint8, device=dev)
             # x, K, Q, dy read; dx written; dK, dQ f32; five [B,T,nh] f32 vectors
             by = (3 * e * B * T * nh * hd + 2 * e * B * T * nh * N + 2 * 4 * B * T * nh * N + 6 * 4 * B * T * nh)

@@ -301,7 +301,7 @@ def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy, *, dD=None, workspace=None, handl
     for t, nm in ((dt, "dt"), (trap, "trap"), (adt, "adt"), (Dh, "Dh"), (dD, "dD")):
         if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
             raise TypeError(f"{nm} must be contiguous float32")
-    need = ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes(Bsz, T, nh, hd, N)
+    need = ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes_for(dtype_code(x.dtype), Bsz, T, nh, hd, N)
     if workspace is None:
         workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     f32 = dict(dtype=torch.float32, device=dev)
