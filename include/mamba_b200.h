@@ -255,9 +255,11 @@ MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream, const mamba
  *   dt (after softplus), trap (after sigmoid), adt = A*dt: [B,T,nh] f32; Dh [nh] f32
  *   ssm_state [B,nh,hd,N], k_state [B,nh,N], v_state [B,nh,hd] f32: written with
  *   the state after the window (NULL = not written); read first when carry_in = 1.
- * 16-bit storage with hd = 64, N = 128 and no carried state runs the chunked
- * form on tcgen05 tensor cores with the running state in TMEM (no chunk-state or
- * K_scaled tensors in HBM); every other case runs the sequential definition.
+ * 16-bit storage with hd <= 64 and N <= 128 (multiples of 8; tiles are padded to
+ * 64 / 128 columns with zeros inside the kernel, so the reference's own limits
+ * hd 32, N 64 are covered) and no carried state runs the chunked form on tcgen05
+ * tensor cores with the running state in TMEM (no chunk-state or K_scaled tensors
+ * in HBM); every other case runs the sequential definition.
  * hd and N are not limited to the reference's hd <= 32, N <= 64
  * (src/mamba3_siso/config.rs:66-99); N <= 128.
  */

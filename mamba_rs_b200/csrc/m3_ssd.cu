@@ -138,6 +138,9 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     const int lane = threadIdx.x & 31, wfull = threadIdx.x >> 5;
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = p.T, nh = p.nh;
+    // headdim <= 64 and d_state <= 128 (multiples of 8): the tiles keep their full
+    // size and the missing columns are zero-filled, so every product is unchanged.
+    const int hdv = p.hd, nsv = p.N;
     constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
     float* vec = reinterpret_cast<float*>(smem + kVec);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBar);
@@ -174,24 +177,28 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     const int r8 = lane & 7, jc = lane >> 3;
     auto issue_qk = [&](const Th* src, uint32_t tile, int c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
-        const Th* base = src + ((static_cast<long long>(b) * T + t0) * nh + h) * NS + 8 * jc;
+        const Th* base = src + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv;
         const uint32_t dst0 = tile + r8 * 16 + jc * 128;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int task = i * 8 + wfull, rg = task >> 2, jg = task & 3, row = rg * 8 + r8;
+            const int col = 8 * jc + 32 * jg;
+            const bool ok = row < nv && col < nsv;
             cp_async16(smem + dst0 + rg * 2048 + jg * 512,
-                       base + static_cast<long long>(min(row, nv - 1)) * nh * NS + 32 * jg, row < nv);
+                       base + static_cast<long long>(min(row, nv - 1)) * nh * nsv + (ok ? col : 0), ok);
         }
     };
     auto issue_v = [&](uint32_t tile, int c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
-        const Th* base = xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD + 8 * jc;
+        const Th* base = xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv;
         const uint32_t dst0 = tile + r8 * 16 + jc * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int task = i * 8 + wfull, rg = task >> 1, jg = task & 1, row = rg * 8 + r8;
+            const int col = 8 * jc + 32 * jg;
+            const bool ok = row < nv && col < hdv;
             cp_async16(smem + dst0 + rg * 1024 + jg * 512,
-                       base + static_cast<long long>(min(row, nv - 1)) * nh * HD + 32 * jg, row < nv);
+                       base + static_cast<long long>(min(row, nv - 1)) * nh * hdv + (ok ? col : 0), ok);
         }
     };
     // Per-row scalars of chunk c into stage `st`: inclusive cumsum of adt, scale, gamma.
@@ -351,7 +358,7 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         // ---- 5. epilogue: y row; 16-bit copy of the new state for the next chunk ----
         {
             const float e_t = ex2(dA[tid] * kLog2e);
-            const long long y_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+            const long long y_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
             const int q2 = half;
             float y1[32], y2[32];
             tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
@@ -363,7 +370,8 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             if (row_ok) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
+                    if (q2 * 32 + 8 * j < hdv)
+                        *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
                         make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
                                    pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
             }
@@ -378,7 +386,8 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             } else if (p.ssm_state) {  // final state [b, h, p, n], n = tid
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                    p.ssm_state[((static_cast<long long>(b) * nh + h) * HD + q2 * 32 + i) * NS + tid] = sv[i];
+                    if (q2 * 32 + i < hdv && tid < nsv)
+                        p.ssm_state[((static_cast<long long>(b) * nh + h) * hdv + q2 * 32 + i) * nsv + tid] = sv[i];
             }
         }
         fence_before();
@@ -388,10 +397,10 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
         const long long last = static_cast<long long>(b) * T + (T - 1);
-        if (p.k_state && half == 0)
-            p.k_state[(static_cast<long long>(b) * nh + h) * NS + tid] = to_f(Kg[(last * nh + h) * NS + tid]);
-        if (p.v_state && half == 0 && tid < HD)
-            p.v_state[(static_cast<long long>(b) * nh + h) * HD + tid] = to_f(xg[last * nh * HD + h * HD + tid]);
+        if (p.k_state && half == 0 && tid < nsv)
+            p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] = to_f(Kg[(last * nh + h) * nsv + tid]);
+        if (p.v_state && half == 0 && tid < hdv)
+            p.v_state[(static_cast<long long>(b) * nh + h) * hdv + tid] = to_f(xg[last * nh * hdv + h * hdv + tid]);
     }
     __syncthreads();
     if (threadIdx.x < 32)
@@ -449,7 +458,8 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
     p.status = c->d_status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd == tc::HD && a.N == tc::NS && !a.carry_in &&
+    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd <= tc::HD && a.hd % 8 == 0 && a.N <= tc::NS &&
+                             a.N % 8 == 0 && !a.carry_in &&
                              !a.force_sequential && al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.y);
     if (tensor_core) {
         dim3 grid(a.nh, a.B);

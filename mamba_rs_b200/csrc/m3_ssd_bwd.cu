@@ -335,6 +335,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     const int tid = threadIdx.x & 127, half = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3, lane = tid & 31;
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = p.T, nh = p.nh;
+    // headdim <= 64, d_state <= 128 (multiples of 8): full-size tiles, missing columns zero-filled
+    const int hdv = p.hd, nsv = p.N;
     constexpr uint32_t fmt = std::is_same<Th, __nv_bfloat16>::value ? 1u : 0u;
     float* dA = reinterpret_cast<float*>(smem + kVec);
     float* scl = dA + 128;
@@ -424,13 +426,15 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     // Cooperative asynchronous load of a [128 x C] tile of 16-bit rows (row stride `ld`
     // elements) into the core-matrix layout; rows >= nv are zero-filled.
     const int r8 = threadIdx.x & 7, jc = (threadIdx.x & 31) >> 3, wfull = threadIdx.x >> 5;
-    auto issue_rows = [&](const Th* base, long long ld, uint32_t tile, int C, int nv) {
+    auto issue_rows = [&](const Th* base, long long ld, uint32_t tile, int C, int cols, int nv) {
         const int jgroups = C / 32;  // groups of four 16-byte pieces per row
         const uint32_t dst0 = tile + r8 * 16 + jc * 128;
         for (int task = wfull; task < 16 * jgroups; task += 8) {
             const int rg = task / jgroups, jg = task - rg * jgroups, row = rg * 8 + r8;
+            const int col = 8 * jc + 32 * jg;
+            const bool ok = row < nv && col < cols;
             cp_async16(smem + dst0 + rg * (C / 8) * 128 + jg * 512,
-                       base + static_cast<long long>(min(row, nv - 1)) * ld + 8 * jc + 32 * jg, row < nv);
+                       base + static_cast<long long>(min(row, nv - 1)) * ld + (ok ? col : 0), ok);
         }
     };
 
@@ -440,8 +444,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const bool last = c + 1 == nc;
         float run = 0.0f, g = 0.0f, s = 0.0f;
         if (!last) {
-            issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kK, NS, nv);
-            issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kV, HD, nv);
+            issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
+            issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
             cp_async_commit();
             load_scalars(t0, nv, run, g, s);
             const float dA_end = dA[nv - 1];
@@ -505,10 +509,10 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const bool row_ok = tid < nv;
         const bool has_sin = c > 0;
         // ---- loads (asynchronous, 8 rows x 64 bytes per warp instruction) under the scalars ----
-        issue_rows(Qg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kQ, NS, nv);
-        issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * NS, static_cast<long long>(nh) * NS, kK, NS, nv);
-        issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kV, HD, nv);
-        issue_rows(dyg + (static_cast<long long>(b) * T + t0) * nh * HD + h * HD, static_cast<long long>(nh) * HD, kDY, HD, nv);
+        issue_rows(Qg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kQ, NS, nsv, nv);
+        issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
+        issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
+        issue_rows(dyg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kDY, HD, hdv, nv);
         if (has_sin) {
             const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
 #pragma unroll
@@ -522,8 +526,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const float e_t = ex2(dA_t * kLog2e), e_end = ex2(dA_end * kLog2e);
         const float lend_t = row_ok ? ex2((dA_end - dA_t) * kLog2e) : 0.0f;
         const float w_t = lend_t * s_t;
-        const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * NS;
-        const long long x_row = (static_cast<long long>(b) * T + t) * nh * HD + h * HD;
+        const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * nsv;
+        const long long x_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
         cp_async_wait_all();
         __syncthreads();
         // E o dY from the landed dY tile (own row, own half of the columns)
@@ -737,9 +741,11 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                             o[2 * u] = fmaf(gp, f.x, av[8 * j + 2 * u]);
                             o[2 * u + 1] = fmaf(gp, f.y, av[8 * j + 2 * u + 1]);
                         }
-                        float4* dst = reinterpret_cast<float4*>(p.dQ + qk_row + q4 * 32 + 8 * j);
-                        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-                        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+                        if (q4 * 32 + 8 * j < nsv) {
+                            float4* dst = reinterpret_cast<float4*>(p.dQ + qk_row + q4 * 32 + 8 * j);
+                            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+                            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+                        }
                     }
                 }
             }
@@ -759,7 +765,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                             const float2 f = unpack2<Th>(w4[u]);
                             o[u] = pack2<Th>(fmaf(dcoef, f.x, av[8 * j + 2 * u]), fmaf(dcoef, f.y, av[8 * j + 2 * u + 1]));
                         }
-                        *reinterpret_cast<uint4*>(dxg + x_row + q2 * 32 + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+                        if (q2 * 32 + 8 * j < hdv)
+                            *reinterpret_cast<uint4*>(dxg + x_row + q2 * 32 + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
             }
@@ -815,7 +822,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
                         o[2 * u] = o0;
                         o[2 * u + 1] = o1;
                     }
-                    if (row_ok) {
+                    if (row_ok && q4 * 32 + 8 * j < nsv) {
                         float4* dst = reinterpret_cast<float4*>(p.dK + qk_row + q4 * 32 + 8 * j);
                         dst[0] = make_float4(o[0], o[1], o[2], o[3]);
                         dst[1] = make_float4(o[4], o[5], o[6], o[7]);
@@ -891,9 +898,9 @@ static size_t m3_bwd_smem(int hd, int N) {
     return sizeof(float) * (3 * kM3C * LQ + 3 * kM3C * LV + 2 * kM3C * LG + 2 * hd * LQ + 12 * 32);
 }
 
-// Tensor-core geometry: 16-bit storage, headdim 64, d_state 128.
+// Tensor-core geometry: 16-bit storage, headdim <= 64, d_state <= 128, both multiples of 8.
 static bool m3_bwd_tc_shape(int dtype, int hd, int N) {
-    return dtype != MAMBA_B200_F32 && hd == tcb::HD && N == tcb::NS;
+    return dtype != MAMBA_B200_F32 && hd <= tcb::HD && hd % 8 == 0 && N <= tcb::NS && N % 8 == 0;
 }
 
 // States first (f32 every 32 steps for the CUDA-core kernel; 16-bit tiles every 128

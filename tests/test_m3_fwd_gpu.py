@@ -89,6 +89,26 @@ def test_tensor_core_kernel_matches_oracle(cuda_dev, shape, dt):
     np.testing.assert_array_equal(vs, ref["v_state"])
 
 
+# the reference's own limits (headdim 32, d_state 64) and other multiples of 8: the
+# kernel pads its tiles to 64 / 128 columns with zeros
+PADDED_SHAPES = [(2, 200, 2, 32, 64), (1, 130, 3, 8, 8), (1, 300, 2, 24, 40), (1, 129, 1, 64, 16), (1, 64, 2, 16, 128)]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", PADDED_SHAPES, ids=lambda s: "B%dT%dnh%dhd%dN%d" % s)
+def test_tensor_core_kernel_with_padded_head_and_state_dims(cuda_dev, shape, dt):
+    B, T, nh, hd, N = shape
+    i = rounded(synth.m3_ssd_inputs(B, T, nh, hd, N, seed=T + hd), dt)
+    ref = oracle.m3_ssd_fwd(*[i[k] for k in ARGS])
+    y, ssm, ks, vs = run_gpu(i, dt, cuda_dev)
+    assert rel_err(y, ref["y"]) <= TOL[dt]
+    assert rel_err(ssm, ref["ssm_state"]) <= TOL[dt]
+    np.testing.assert_array_equal(ks, ref["k_state"])
+    np.testing.assert_array_equal(vs, ref["v_state"])
+    y2, ssm2, _, _ = run_gpu(i, dt, cuda_dev, force_sequential=True)
+    assert rel_err(y, y2) <= TOL[dt]
+
+
 def test_tensor_core_and_sequential_kernels_agree(cuda_dev):
     i = rounded(synth.m3_ssd_inputs(2, 520, 4, 64, 128, seed=9), "bf16")
     y1, s1, _, _ = run_gpu(i, "bf16", cuda_dev)
