@@ -42,6 +42,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--save-stride", type=int, default=32)
     ap.add_argument("--a-mode", default="s4d", choices=["s4d", "random"])
+    ap.add_argument("--heads", type=int, default=32, help="Mamba-3: number of heads")
+    ap.add_argument("--headdim", type=int, default=64, help="Mamba-3: head dimension")
+    ap.add_argument("--dstate", type=int, default=128, help="Mamba-3: state size")
+    ap.add_argument("--sequential", action="store_true", help="Mamba-3 forward: the sequential kernel")
     args = ap.parse_args()
 
     import torch
@@ -58,7 +62,7 @@ def main():
     cfg, by, fn = {}, 0, None
 
     if args.op.startswith("m3_"):
-        B, T, nh, hd, N = args.batch or 8, 4096, 32, 64, 128
+        B, T, nh, hd, N = args.batch or 8, 4096, args.heads, args.headdim, args.dstate
         i = synth.m3_ssd_inputs(B, T, nh, hd, N, seed=0)
         a = [t(i[k], bf if k in ("x", "K", "Q") else None) for k in ("x", "K", "Q", "dt", "trap", "adt", "Dh")]
         cfg = dict(B=B, T=T, nh=nh, hd=hd, N=N, storage="bf16")
@@ -66,7 +70,7 @@ def main():
             y = torch.empty_like(a[0])
             ssm = torch.zeros(B, nh, hd, N, device=dev)
             by = synth.m3_fwd_algorithmic_bytes(B, T, nh, hd, N, e)
-            fn = lambda: mb.m3_ssd_fwd(*a, ssm_state=ssm, y=y)
+            fn = lambda: mb.m3_ssd_fwd(*a, ssm_state=ssm, y=y, force_sequential=args.sequential)
         else:
             dy = torch.randn(B, T, nh * hd, device=dev).to(bf)
             ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes_for(2, B, T, nh, hd, N),
