@@ -361,11 +361,12 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             const long long y_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
             const int q2 = half;
             float y1[32], y2[32];
-            tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
             if (c > 0) {
-                tmem_ld32(lane_addr + cY2 + q2 * 32, y2);
+                tmem_ld32x2(lane_addr + cY1 + q2 * 32, y1, lane_addr + cY2 + q2 * 32, y2);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) y1[i] = fmaf(e_t, y2[i], y1[i]);
+            } else {
+                tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
             }
             if (row_ok) {
 #pragma unroll

@@ -577,8 +577,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         auto mask_block = [&](auto diag_tag, int q4) {
             constexpr bool DIAG = decltype(diag_tag)::value;
             float gv[32], pv[32];
-            tmem_ld32(lane_addr + c0 + q4 * 32, gv);
-            tmem_ld32(lane_addr + c1 + q4 * 32, pv);
+            tmem_ld32x2(lane_addr + c0 + q4 * 32, gv, lane_addr + c1 + q4 * 32, pv);
             uint32_t pk1[16], pk2[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
@@ -651,13 +650,12 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         if (has_ds) {
             {
                 const int q2 = half;
-                float wv[32];
-                tmem_ld32(lane_addr + c3 + q2 * 32, wv);  // W row s = tid -> w_s W
+                float wv[32], dv[32];
+                // W row s = tid -> w_s W;  dS^T row n = tid
+                tmem_ld32x2(lane_addr + c3 + q2 * 32, wv, lane_addr + cDS + q2 * 32, dv);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) wv[i] *= w_t;
                 tmem_st32(lane_addr + c3 + q2 * 32, wv);
-                float dv[32];
-                tmem_ld32(lane_addr + cDS + q2 * 32, dv);  // dS^T row n = tid
                 if (has_sin) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -706,8 +704,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         auto colsum_block = [&](auto diag_tag, int q4) {
             constexpr bool DIAG = decltype(diag_tag)::value;
             float gv[32], pv[32];
-            tmem_ld32(lane_addr + c0 + q4 * 32, gv);
-            tmem_ld32(lane_addr + c1 + q4 * 32, pv);
+            tmem_ld32x2(lane_addr + c0 + q4 * 32, gv, lane_addr + c1 + q4 * 32, pv);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
                 const float4 da4 = *reinterpret_cast<const float4*>(dAl + q4 * 32 + i);
@@ -798,8 +795,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
             const float gp = g_t * pd;
             for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 float av[32], uv[32];
-                tmem_ld32(lane_addr + c0 + q4 * 32, av);
-                if (has_ds) tmem_ld32(lane_addr + c1 + q4 * 32, uv);
+                if (has_ds) tmem_ld32x2(lane_addr + c0 + q4 * 32, av, lane_addr + c1 + q4 * 32, uv);
+                else tmem_ld32(lane_addr + c0 + q4 * 32, av);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + chunk_off(tid, q4 * 4 + j, NS));
