@@ -149,8 +149,8 @@ typedef struct mamba_b200_sscan_bwd_args {
     const float* a_neg;
     const float* Dp;
     const float* chunk_states; /* [B, ceil(T/save_stride), D, N] from the forward */
-    int save_stride;           /* 32 or 64, as given to the forward; with 32 every CTA of a
-                                  model-sized launch stays resident (about 1.8x faster at d_state 16) */
+    int save_stride;           /* 32 or 64, as given to the forward; 32 is the native setting, a
+                                  stride-64 save is first rebuilt to stride 32 (about 20 % slower) */
     const void* dy;            /* [B*T, ld_dy] gradient w.r.t. the forward output */
     long long ld_dy;
     void* d_u;

@@ -389,6 +389,50 @@ __global__ void bwd_reduce_params_kernel(const float* __restrict__ part_a,
     }
 }
 
+// States entering every 32-step block from states saved every 64 steps: one
+// warp per (sample, 64-step block, 16 channels), two lanes per channel as in the
+// two-lane backward, 32 forward steps from the saved state.  Lets a stride-64
+// save run the stride-32 backward (whose CTAs all fit the GPU at once).
+template <typename Tact>
+__global__ void __launch_bounds__(32) sscan_densify_kernel(const BwdParams p, float* __restrict__ dense,
+                                                           int softplus) {
+    const int lane = threadIdx.x, part = lane >> 4, chl = lane & 15;
+    const int d = blockIdx.x * 16 + chl, k = blockIdx.y, b = blockIdx.z, n0 = part * 8;
+    const int T = p.T, D = p.D, N = p.N;
+    if (d >= D) return;
+    const int nb64 = (T + 63) / 64, nb32 = (T + 31) / 32;
+    float h[8], a2[8];
+    const float* cs = p.chunk_states + ((static_cast<long long>(b) * nb64 + k) * D + d) * N;
+    float* o0 = dense + ((static_cast<long long>(b) * nb32 + 2 * k) * D + d) * N;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const bool ok = n0 + j < N;
+        h[j] = ok ? cs[n0 + j] : 0.0f;
+        a2[j] = ok ? p.a_neg[static_cast<long long>(d) * N + n0 + j] * kLog2e : 0.0f;
+        if (ok) o0[n0 + j] = h[j];
+    }
+    const int t0 = 64 * k;
+    if (t0 + 32 >= T) return;  // no second 32-step block inside this one
+    const Tact* ub = static_cast<const Tact*>(p.u) + (static_cast<long long>(b) * T + t0) * p.ld_u + d;
+    const Tact* db = static_cast<const Tact*>(p.dl) + (static_cast<long long>(b) * T + t0) * p.ld_dl + d;
+    const Tact* bb = static_cast<const Tact*>(p.bm) + (static_cast<long long>(b) * T + t0) * p.ld_bc + n0;
+#pragma unroll 4
+    for (int r = 0; r < 32; ++r) {
+        float dl = to_f(db[static_cast<long long>(r) * p.ld_dl]);
+        if (softplus) dl = softplusf_fast(dl);
+        const float du = dl * to_f(ub[static_cast<long long>(r) * p.ld_u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float bv = n0 + j < N ? to_f(bb[static_cast<long long>(r) * p.ld_bc + j]) : 0.0f;
+            h[j] = fmaf(ex2(dl * a2[j]), h[j], du * bv);
+        }
+    }
+    float* o1 = o0 + static_cast<long long>(D) * N;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (n0 + j < N) o1[n0 + j] = h[j];
+}
+
 template <typename Tact, int NS>
 static void fill_bwd(BwdKernelFn* f, size_t* smem) {
     f[0] = sscan_bwd_kernel<Tact, NS, 0>;
@@ -469,7 +513,8 @@ int m1_bwd_configure(Ctx* c) {
 
 static int bwd_ns(int N) { return N <= 4 ? 4 : (N <= 8 ? 8 : 16); }
 
-static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off_d, size_t* total) {
+static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off_d, size_t* off_dense,
+                          size_t* total) {
     // channel tiles of the dB/dC partials: 16 channels per CTA for the two-lane
     // kernel (d_state > 8), 32 for the one-lane kernel
     const size_t tiles = N > 8 ? (D + 15) / 16 : (D + 31) / 32, V = 2 * bwd_ns(N);
@@ -480,7 +525,10 @@ static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off
     const size_t dd = sizeof(float) * static_cast<size_t>(B) * D;
     *off_a = bc;
     *off_d = bc + a;
-    *total = bc + a + ((dd + 255) & ~size_t(255));
+    *off_dense = bc + a + ((dd + 255) & ~size_t(255));
+    // states every 32 steps, rebuilt from a stride-64 save (two-lane kernel only)
+    const size_t dense = N > 8 ? sizeof(float) * static_cast<size_t>(B) * ((T + 31) / 32) * D * N : 0;
+    *total = *off_dense + ((dense + 255) & ~size_t(255));
 }
 
 }  // namespace mb200
@@ -489,8 +537,8 @@ using namespace mb200;
 
 extern "C" MAMBA_B200_API long long mamba_b200_sscan_bwd_workspace_bytes(int B, int T, int D, int N) {
     if (B <= 0 || T <= 0 || D <= 0 || N <= 0 || N > 16) return 0;
-    size_t a, d, total;
-    bwd_ws_layout(B, T, D, N, &a, &d, &total);
+    size_t a, d, dn, total;
+    bwd_ws_layout(B, T, D, N, &a, &d, &dn, &total);
     return static_cast<long long>(total);
 }
 
@@ -516,8 +564,8 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     if (a.ld_u < a.D || a.ld_delta < a.D || a.ld_dy < a.D || a.ld_bc < a.N || a.ld_du < a.D ||
         a.ld_ddelta < a.D || (a.z_mode && (a.ld_z < a.D || a.ld_dz < a.D)))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: a row stride is smaller than its row");
-    size_t off_a, off_d, total;
-    bwd_ws_layout(a.B, a.T, a.D, a.N, &off_a, &off_d, &total);
+    size_t off_a, off_d, off_dense, total;
+    bwd_ws_layout(a.B, a.T, a.D, a.N, &off_a, &off_d, &off_dense, &total);
     if (a.workspace_bytes < static_cast<long long>(total))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: workspace %lld < %zu bytes", a.workspace_bytes, total);
     if (reinterpret_cast<uintptr_t>(a.workspace) % 256)
@@ -537,10 +585,23 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     p.part_d = reinterpret_cast<float*>(ws + off_d);
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.S = a.save_stride; p.z_mode = a.z_mode;
     p.status = c->d_status;
-    const int S = a.save_stride;
     // one lane per channel for d_state <= 8 (and on request, for comparison)
     static const bool one_lane_env = getenv("MAMBA_B200_BWD_ONE_LANE") != nullptr;
+    static const bool native64_env = getenv("MAMBA_B200_BWD_NATIVE_64") != nullptr;
     const bool two_lane = a.N > 8 && !one_lane_env;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int S = a.save_stride;
+    if (two_lane && S == 64 && !native64_env) {
+        // rebuild the states at the odd 32-step boundaries, then run the stride-32 kernel
+        float* dense = reinterpret_cast<float*>(ws + off_dense);
+        dim3 dg((a.D + 15) / 16, (a.T + 63) / 64, a.B);
+        if (a.dtype == MAMBA_B200_F32) sscan_densify_kernel<float><<<dg, 32, 0, st>>>(p, dense, a.delta_softplus);
+        else if (a.dtype == MAMBA_B200_F16) sscan_densify_kernel<__half><<<dg, 32, 0, st>>>(p, dense, a.delta_softplus);
+        else sscan_densify_kernel<__nv_bfloat16><<<dg, 32, 0, st>>>(p, dense, a.delta_softplus);
+        MB200_CUDA_CHECK(c, cudaGetLastError());
+        p.chunk_states = dense;
+        p.S = S = 32;
+    }
     const int DT = two_lane ? 16 : 32;  // channels per CTA
     unsigned m = 0;
     if (make_tmap_3d(c, &p.tm_u, a.dtype, a.u, a.ld_u, a.D, a.T, a.B, DT, S)) m |= kBU;
@@ -556,7 +617,6 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     }
     p.tma_mask = m;
 
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     const BwdTable& t = bwd_table();
     const int flags = (a.delta_softplus ? 1 : 0) | (a.z_mode ? 2 : 0);
     const int tiles = (a.D + DT - 1) / DT;
