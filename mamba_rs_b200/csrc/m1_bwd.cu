@@ -416,16 +416,44 @@ __global__ void __launch_bounds__(32) sscan_densify_kernel(const BwdParams p, fl
     const Tact* ub = static_cast<const Tact*>(p.u) + (static_cast<long long>(b) * T + t0) * p.ld_u + d;
     const Tact* db = static_cast<const Tact*>(p.dl) + (static_cast<long long>(b) * T + t0) * p.ld_dl + d;
     const Tact* bb = static_cast<const Tact*>(p.bm) + (static_cast<long long>(b) * T + t0) * p.ld_bc + n0;
+    // arithmetic-progression rows of a_neg (the S4D init): two exp2 per step instead of eight
+    bool geo = true;
+    const float step = a2[1] - a2[0];
+#pragma unroll
+    for (int j = 2; j < 8; ++j)
+        if (fabsf(a2[j] - fmaf(static_cast<float>(j), step, a2[0])) > 4.8e-7f * fabsf(a2[j])) geo = false;
+    geo = __all_sync(__activemask(), geo ? 1 : 0) != 0;
+    const bool vec_b = N == 16 && (p.ld_bc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.bm) % 16) == 0;
 #pragma unroll 4
     for (int r = 0; r < 32; ++r) {
         float dl = to_f(db[static_cast<long long>(r) * p.ld_dl]);
         if (softplus) dl = softplusf_fast(dl);
         const float du = dl * to_f(ub[static_cast<long long>(r) * p.ld_u]);
+        float bv[8], e[8];
+        if (vec_b) {
+            StateVec<Tact, 8> q;
+            q.load(bb + static_cast<long long>(r) * p.ld_bc);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float bv = n0 + j < N ? to_f(bb[static_cast<long long>(r) * p.ld_bc + j]) : 0.0f;
-            h[j] = fmaf(ex2(dl * a2[j]), h[j], du * bv);
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = q.pair(j);
+                bv[2 * j] = f.x;
+                bv[2 * j + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) bv[j] = n0 + j < N ? to_f(bb[static_cast<long long>(r) * p.ld_bc + j]) : 0.0f;
         }
+        if (geo) {
+            const float R = ex2(dl * step);
+            e[0] = ex2(dl * a2[0]);
+#pragma unroll
+            for (int j = 1; j < 8; ++j) e[j] = e[j - 1] * R;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = ex2(dl * a2[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = fmaf(e[j], h[j], du * bv[j]);
     }
     float* o1 = o0 + static_cast<long long>(D) * N;
 #pragma unroll
