@@ -19,7 +19,9 @@
 //     shuffle butterfly (15 shuffles) that leaves one of the 32 sums in each
 //     lane: one coalesced 128-byte store per step into the per-channel-tile
 //     partials;
-//   * du / ddelta / dz leave as 32-byte segments straight from registers.
+//   * du / ddelta / dz leave as 32-byte segments straight from registers; rows are
+//     finished in pairs (lanes 0-15 the even row, lanes 16-31 the odd one), so the
+//     elementwise output code runs once per two rows without divergence.
 // Results differ from the one-lane kernel only by summation order.
 #pragma once
 #include <string.h>
@@ -92,6 +94,7 @@ struct Bwd2Traits {
     static constexpr size_t OFF_ENT = OFF_RAWB;                                   // f32 [NSUB-1][8][32]
     static constexpr size_t OFF_BAR = OFF_ENT + mx(2 * BCR, sizeof(float) * (NSUB - 1) * 8 * THREADS);
     static constexpr size_t SMEM = OFF_BAR + 128;
+    static_assert(SB % 2 == 0, "rows are finished in pairs");
 };
 
 // FLAGS: bit0 softplus on delta, bit1 gate present.
@@ -298,6 +301,7 @@ __global__ void __maxnreg__(MB200_BWD2_REGS) sscan_bwd2_kernel(const __grid_cons
                 }
                 float* pbc = p.part_bc + (((static_cast<long long>(b) * gridDim.x + tile) * T) + t0 + r_lo) * 32 +
                              ((chl & 8) ? 16 : 0) + n0 + (chl & 7);
+                float hB = 0.0f, hA = 0.0f, hY = 0.0f;  // sums of the odd row of a pair
 #pragma unroll
                 for (int i = SB - 1; i >= 0; --i) {
                     const int r = r_lo + i;
@@ -336,24 +340,31 @@ __global__ void __maxnreg__(MB200_BWD2_REGS) sscan_bwd2_kernel(const __grid_cons
                     sB += __shfl_xor_sync(0xffffffffu, sB, 16);
                     sA += __shfl_xor_sync(0xffffffffu, sA, 16);
                     if (kGate) ys += __shfl_xor_sync(0xffffffffu, ys, 16);
-                    const bool row_ok = d_ok && r < nv;
-                    const long long grow = static_cast<long long>(b) * T + t0 + r;
-                    if (part == 0) {
-                        if (row_ok) g_du[grow * p.ld_du + d] = from_f<Tact>(fmaf(dyp, Dd, dlv * sB));
-                        accD = fmaf(dyp, uv, accD);
+                    // Elementwise outputs, two rows at a time: the sums of the odd row wait
+                    // for the even row below it, then lanes 0-15 finish the even row and
+                    // lanes 16-31 the odd one with the same instructions.
+                    if (i & 1) {
+                        hB = sB; hA = sA; hY = ys;
+                    } else {
+                        const int rm = r + part;
+                        const float mB = part ? hB : sB, mA = part ? hA : sA, mY = part ? hY : ys;
+                        const float m_dl = rdl[rm * DT], m_u = to_f(ru[rm * DT]), m_dyp = rgy[rm * DT];
+                        const bool row_ok = d_ok && rm < nv;
+                        const long long grow = static_cast<long long>(b) * T + t0 + rm;
+                        if (row_ok) g_du[grow * p.ld_du + d] = from_f<Tact>(fmaf(m_dyp, Dd, m_dl * mB));
+                        accD = fmaf(m_dyp, m_u, accD);
                         if (kGate) {
-                            const float zv = to_f(st_z(s)[r * DT + col]);
-                            const float dyv = to_f(st_dy(s)[r * DT + col]);
+                            const float zv = to_f(st_z(s)[rm * DT + col]);
+                            const float dyv = to_f(st_dy(s)[rm * DT + col]);
                             const float sg = sigmoidf_fast(zv);
                             const float dsilu = sg * fmaf(zv, 1.0f - sg, 1.0f);
                             // pre-gate output and the gate, kernels/elementwise.cu:191-233
                             if (row_ok)
-                                g_dz[grow * p.ld_dz + d] = from_f<Tact>(dyv * fmaf(Dd, uv, ys) * (gate_is_silu ? dsilu : 1.0f));
+                                g_dz[grow * p.ld_dz + d] = from_f<Tact>(dyv * fmaf(Dd, m_u, mY) * (gate_is_silu ? dsilu : 1.0f));
                         }
-                    } else {
-                        float ddl = fmaf(sA, kLn2, uv * sB);
+                        float ddl = fmaf(mA, kLn2, m_u * mB);
                         if (kSoftplus) {
-                            const float raw = to_f(st_dl(s)[r * DT + col]);
+                            const float raw = to_f(st_dl(s)[rm * DT + col]);
                             ddl *= raw > 20.0f ? 1.0f : sigmoidf_fast(raw);  // activations.cu:68-104
                         }
                         if (row_ok) g_ddl[grow * p.ld_ddl + d] = from_f<Tact>(ddl);
