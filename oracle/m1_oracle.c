@@ -14,9 +14,12 @@
  *   (fast_exp accuracy and edge cases of src/ops/fast_math.rs:263-341, the
  *   step == batched == prefill identities of tests/prefill.rs:90-168, the
  *   f64 finite-difference gradient check of tests/grad_oracle.rs) and, on a
- *   GPU box, against the reference's own CUDA kernels compiled from its
- *   sources (oracle/_ref).  Bit-level parity with a build of the Rust CPU
- *   code itself is UNPINNED.
+ *   GPU box, against the reference's own CUDA kernels compiled unchanged from
+ *   its sources (oracle/_ref): scan forward (parallel and sequential), scan
+ *   backward (ssm_parallel_scan_bwd_*, ssm_backward_local_* and the four
+ *   reducers), conv1d forward and backward, within 1e-4 (f32) / 2e-2 (16-bit
+ *   storage).  Bit-level parity with a build of the Rust CPU code itself is
+ *   UNPINNED.
  *
  * Build: make -C oracle   (gcc -O2 -ffp-contract=off: Rust never contracts
  * a*b+c into an fma, so neither may the C compiler.)
@@ -146,7 +149,8 @@ static void m1_fwd_sample(const OrcM1Shape *s, const float *x, const float *delt
                           const float *a_neg, const float *Dp, const float *conv_w,
                           const float *conv_b, float *conv_state, float *ssm_state,
                           float *y, float *u_out, float *dl_out, float *pc_out,
-                          float *yssm_out, float *h_all, int d_begin, int d_end) {
+                          float *yssm_out, float *h_all, int d_begin, int d_end,
+                          int train_form) {
     const int T = s->T, D = s->D, N = s->N, K = s->K;
     float *da = (float *)malloc(sizeof(float) * (size_t)(N > 8 ? N : 8));
     if (h_all)
@@ -173,7 +177,12 @@ static void m1_fwd_sample(const OrcM1Shape *s, const float *x, const float *delt
             if (dl_out) dl_out[(size_t)t * D + d] = dl;
             float du = dl * u;
             for (int n = 0; n < N; n++) da[n] = dl * a_neg[(size_t)d * N + n];
-            orc_fast_exp_inplace(da, N);
+            /* prefill.rs:287 exponentiates d_state * SSM_BLOCK lanes at once (always a
+             * multiple of 8: every lane takes the AVX2 form); the training forward
+             * (cpu/forward.rs:246-249) exponentiates the d_state values of one channel
+             * (AVX2 body, scalar tail). */
+            if (train_form) orc_fast_exp_inplace(da, N);
+            else for (int n = 0; n < N; n++) da[n] = orc_fast_exp_simd_lane(da[n]);
             const float *Bt = Bm + (size_t)t * s->ld_bc;
             const float *Ct = Cm + (size_t)t * s->ld_bc;
             float acc = 0.0f;
@@ -210,7 +219,7 @@ ORC_API int orc_m1_fused_fwd(const OrcM1Shape *s, const float *x, const float *d
                       s->K ? conv_state + b * D * s->K : NULL, ssm_state + b * D * N,
                       y + b * T * s->ld_y, u_out ? u_out + b * T * D : NULL,
                       dl_out ? dl_out + b * T * D : NULL, NULL, NULL,
-                      h_all ? h_all + b * (T + 1) * D * N : NULL, d_begin, d_end);
+                      h_all ? h_all + b * (T + 1) * D * N : NULL, d_begin, d_end, 0);
       }
     return 0;
 }
@@ -263,7 +272,7 @@ ORC_API int orc_m1_fused_bwd(const OrcM1Shape *s, const float *x, const float *d
         const float *Bb = Bm + b * T * s->ld_bc, *Cb = Cm + b * T * s->ld_bc;
         const float *zb = s->has_z ? z + b * T * s->ld_z : NULL;
         m1_fwd_sample(&sp, xb, db, Bb, Cb, zb, a_neg, Dp, conv_w, conv_b, cs, hs, yg, u, dl,
-                      pc, ys, h_all, 0, (int)D);
+                      pc, ys, h_all, 0, (int)D, 1);
         const float *dgb = dg + b * T * D;
         /* gating backward, backward.rs:62-82 */
         for (size_t i = 0; i < T * D; i++) {
@@ -613,7 +622,7 @@ ORC_API int orc_m1_prefill(const OrcM1Config *c, const float *w, const float *in
         if (tap_xdbl) memcpy(tap_xdbl + (long)l * T * xd, xdbl, sizeof(float) * T * xd);
         /* F4a(again, carrying the real state)+F4c softplus+F4d+F4e: the fused op */
         m1_fwd_sample(&s, proj, draw, xdbl + dr, xdbl + dr + N, proj + di, v.a_neg, v.d_param,
-                      v.conv_w, v.conv_b, cs, hs, yg, NULL, NULL, NULL, NULL, NULL, 0, (int)di);
+                      v.conv_w, v.conv_b, cs, hs, yg, NULL, NULL, NULL, NULL, NULL, 0, (int)di, 0);
         if (tap_gated) memcpy(tap_gated + (long)l * T * di, yg, sizeof(float) * T * di);
         gemm_ref(o, yg, v.out_proj_w, NULL, T, di, dm); /* F5 */
         for (long i = 0; i < T * dm; i++) out[i] += o[i]; /* F6 */
