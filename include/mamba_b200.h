@@ -55,6 +55,12 @@ MAMBA_B200_API const char* mamba_b200_last_error(void* handle);
 /* Synchronously reads the device status word (bounded waits that gave up).
  * Returns 0 or MAMBA_B200_ERR_KERNEL.  Not graph-capturable; optional. */
 MAMBA_B200_API int mamba_b200_check_status(void* handle, void* stream);
+/* Diagnostic with no counterpart in the reference: launches one tiny kernel whose only
+ * thread waits, for at most max_polls (1..100000) polls, on a barrier that nothing
+ * signals.  The wait gives up, the kernel returns normally, and the next
+ * mamba_b200_check_status reports MAMBA_B200_ERR_KERNEL once and clears the word:
+ * the path every bounded wait of the library takes when it runs out. */
+MAMBA_B200_API int mamba_b200_selftest_wait_timeout(void* handle, void* stream, int max_polls);
 
 /*
  * Mamba-1 fused forward:

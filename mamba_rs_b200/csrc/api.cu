@@ -72,20 +72,14 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     MB200_CUDA_CHECK(c, cudaMalloc(&c->d_status, sizeof(int)));
     MB200_CUDA_CHECK(c, cudaMemset(c->d_status, 0, sizeof(int)));
     int rc = MAMBA_B200_OK;
-#ifndef MB200_BWD_TUNING  // tuning builds link one kernel family only
     rc = m1_fwd_configure(c);
     if (rc) return rc;
-#endif
-#ifndef MB200_FWD_TUNING
     rc = m1_bwd_configure(c);
     if (rc) return rc;
-#endif
-#if !defined(MB200_FWD_TUNING) && !defined(MB200_BWD_TUNING)
     rc = m3_configure(c);
     if (rc) return rc;
     rc = m3_bwd_configure(c);
     if (rc) return rc;
-#endif
     return MAMBA_B200_OK;
 }
 
@@ -108,6 +102,11 @@ extern "C" MAMBA_B200_API const char* mamba_b200_last_error(void* handle) {
 extern "C" MAMBA_B200_API int mamba_b200_check_status(void* handle, void* stream) {
     Ctx* c = static_cast<Ctx*>(handle);
     if (!c) return MAMBA_B200_ERR_ARG;
+    int cur = -1;
+    MB200_CUDA_CHECK(c, cudaGetDevice(&cur));
+    if (cur != c->device)
+        return fail(c, MAMBA_B200_ERR_DEVICE, "check_status: the handle belongs to device %d but device %d is current",
+                    c->device, cur);
     int st = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     MB200_CUDA_CHECK(c, cudaMemcpyAsync(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -116,5 +115,29 @@ extern "C" MAMBA_B200_API int mamba_b200_check_status(void* handle, void* stream
         cudaMemsetAsync(c->d_status, 0, sizeof(int), s);
         return fail(c, MAMBA_B200_ERR_KERNEL, "a kernel gave up a bounded wait (status %d)", st);
     }
+    return MAMBA_B200_OK;
+}
+
+namespace mb200 {
+// One thread waits on an mbarrier that nothing ever arrives on, with a small poll
+// limit: the wait gives up, records the time-out in the status word and the kernel
+// returns normally.
+__global__ void wait_timeout_selftest_kernel(int* status, int max_polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+        mbar_wait(&bar, 0, status, max_polls);
+    }
+}
+}  // namespace mb200
+
+extern "C" MAMBA_B200_API int mamba_b200_selftest_wait_timeout(void* handle, void* stream, int max_polls) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (max_polls < 1 || max_polls > 100000)
+        return fail(c, MAMBA_B200_ERR_ARG, "selftest_wait_timeout: max_polls %d outside 1..100000", max_polls);
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->d_status, max_polls);
+    MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;
 }

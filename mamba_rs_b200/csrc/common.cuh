@@ -87,17 +87,9 @@ __device__ __forceinline__ float softplusf_fast(float v) {
 }
 
 // ---- packed f32x2 arithmetic (one issue slot for two lanes of FP32 work) ----
-#ifndef MB200_NO_F32X2
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-#else
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
-#endif
 __device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
 
 // ---- B / C vectors ------------------------------------------------------------
@@ -160,12 +152,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
-// Bounded wait: gives up after ~2^22 polls (each poll suspends for a
+// Bounded wait: gives up after max_polls polls (each poll suspends for a
 // hardware-chosen time), records kStatusBarrierTimeout and returns false so the
 // kernel can run to its end instead of hanging.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+constexpr int kMbarMaxPolls = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status,
+                                          int max_polls = kMbarMaxPolls) {
     uint32_t ok = 0;
-    for (int it = 0; it < (1 << 22); ++it) {
+    for (int it = 0; it < max_polls; ++it) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"

@@ -475,10 +475,11 @@ struct BwdTable {
     size_t smem[3][3];
 };
 
+// Built once, under the thread-safe initialisation of a function-local static.
 static const BwdTable& bwd_table() {
-    static BwdTable t;
-    static bool init = false;
-    if (!init) {
+    static const BwdTable table = [] {
+        BwdTable t;
+        memset(&t, 0, sizeof(t));
         fill_bwd<float, 4>(t.fn[0][0], &t.smem[0][0]);
         fill_bwd<float, 8>(t.fn[0][1], &t.smem[0][1]);
         fill_bwd<float, 16>(t.fn[0][2], &t.smem[0][2]);
@@ -488,9 +489,9 @@ static const BwdTable& bwd_table() {
         fill_bwd<__nv_bfloat16, 4>(t.fn[2][0], &t.smem[2][0]);
         fill_bwd<__nv_bfloat16, 8>(t.fn[2][1], &t.smem[2][1]);
         fill_bwd<__nv_bfloat16, 16>(t.fn[2][2], &t.smem[2][2]);
-        init = true;
-    }
-    return t;
+        return t;
+    }();
+    return table;
 }
 
 // Two-lane kernels (8 < d_state <= 16): [dtype][stride index][flags].
@@ -500,20 +501,15 @@ struct Bwd2Table {
 };
 
 static const Bwd2Table& bwd2_table() {
-    static Bwd2Table t;
-    static bool init = false;
-    if (!init) {
-#ifdef MB200_BWD_TUNING  // bf16 only: the other dtypes alias it and must not be launched
-        bwd2_kernels_bf16(t.fn[MAMBA_B200_F32], t.smem[MAMBA_B200_F32]);
-        bwd2_kernels_bf16(t.fn[MAMBA_B200_F16], t.smem[MAMBA_B200_F16]);
-#else
+    static const Bwd2Table table = [] {
+        Bwd2Table t;
+        memset(&t, 0, sizeof(t));
         bwd2_kernels_f32(t.fn[MAMBA_B200_F32], t.smem[MAMBA_B200_F32]);
         bwd2_kernels_f16(t.fn[MAMBA_B200_F16], t.smem[MAMBA_B200_F16]);
-#endif
         bwd2_kernels_bf16(t.fn[MAMBA_B200_BF16], t.smem[MAMBA_B200_BF16]);
-        init = true;
-    }
-    return t;
+        return t;
+    }();
+    return table;
 }
 
 int m1_bwd_configure(Ctx* c) {
@@ -613,13 +609,11 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     p.part_d = reinterpret_cast<float*>(ws + off_d);
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.S = a.save_stride; p.z_mode = a.z_mode;
     p.status = c->d_status;
-    // one lane per channel for d_state <= 8 (and on request, for comparison)
-    static const bool one_lane_env = getenv("MAMBA_B200_BWD_ONE_LANE") != nullptr;
-    static const bool native64_env = getenv("MAMBA_B200_BWD_NATIVE_64") != nullptr;
-    const bool two_lane = a.N > 8 && !one_lane_env;
+    // one lane per channel for d_state <= 8, two lanes above
+    const bool two_lane = a.N > 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int S = a.save_stride;
-    if (two_lane && S == 64 && !native64_env) {
+    if (two_lane && S == 64) {
         // rebuild the states at the odd 32-step boundaries, then run the stride-32 kernel
         float* dense = reinterpret_cast<float*>(ws + off_dense);
         dim3 dg((a.D + 15) / 16, (a.T + 63) / 64, a.B);

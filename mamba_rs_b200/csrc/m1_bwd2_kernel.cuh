@@ -31,14 +31,12 @@
 #include "common.cuh"
 #include "internal.h"
 
-#ifndef MB200_BWD2_SB
-#define MB200_BWD2_SB 4
-#endif
-#ifndef MB200_BWD2_REGS
-#define MB200_BWD2_REGS 168
-#endif
-
 namespace mb200 {
+
+// Steps per sub-block of the reverse sweep, and the register cap that lets 11-12
+// one-warp CTAs share an SM (both found by measurement on B200).
+constexpr int kBwd2SubBlock = 4;
+constexpr int kBwd2MaxRegs = 168;
 
 struct BwdParams {
     CUtensorMap tm_u, tm_dl, tm_z, tm_dy, tm_b, tm_c, tm_du, tm_ddl, tm_dz;
@@ -77,7 +75,7 @@ __device__ __forceinline__ void bwd_load_plain(Tact* dst, const Tact* src, long 
 
 template <typename Tact, int S>
 struct Bwd2Traits {
-    static constexpr int DT = 16, THREADS = 32, SB = MB200_BWD2_SB, NSUB = S / SB, NP = 16;
+    static constexpr int DT = 16, THREADS = 32, SB = kBwd2SubBlock, NSUB = S / SB, NP = 16;
     static constexpr size_t al(size_t v) { return (v + 127) & ~size_t(127); }
     static constexpr size_t mx(size_t a, size_t b) { return a > b ? a : b; }
     static constexpr size_t ACT = al(sizeof(Tact) * S * DT);
@@ -99,7 +97,7 @@ struct Bwd2Traits {
 
 // FLAGS: bit0 softplus on delta, bit1 gate present.
 template <typename Tact, int S, int FLAGS>
-__global__ void __maxnreg__(MB200_BWD2_REGS) sscan_bwd2_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __maxnreg__(kBwd2MaxRegs) sscan_bwd2_kernel(const __grid_constant__ BwdParams p) {
     using Tr = Bwd2Traits<Tact, S>;
     constexpr bool kSoftplus = (FLAGS & 1) != 0, kGate = (FLAGS & 2) != 0;
     constexpr int DT = 16, SB = Tr::SB, NSUB = Tr::NSUB, NP = 16, THREADS = 32;

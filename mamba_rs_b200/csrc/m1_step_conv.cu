@@ -6,6 +6,7 @@
 // once (plus a K-1 row halo per time chunk).
 #include <string.h>
 
+#include <atomic>
 #include <initializer_list>
 
 #include "common.cuh"
@@ -27,6 +28,7 @@ struct StepParams {
     const float *a_neg, *Dp, *conv_w, *conv_b;
     float *conv_state, *ssm_state;
     int B, D, N, K, delta_softplus, z_mode;
+    int vec_state;  // a_neg and ssm_state rows may be moved as float4 (N % 4 == 0, 16-byte aligned bases)
 };
 
 template <typename Tact>
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(128) sscan_step_kernel(const StepParams p) {
     const float* a = p.a_neg + static_cast<long long>(d) * p.N;
     float y = 0.0f;
     int n = 0;
-    if ((p.N & 3) == 0) {
+    if (p.vec_state) {
         for (; n < p.N; n += 4) {
             float4 hv = *reinterpret_cast<float4*>(h + n);
             const float4 av = *reinterpret_cast<const float4*>(a + n);
@@ -239,20 +241,10 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const ConvParams p) {
 // and deeper unrolling cost more in registers (occupancy) than they save.
 // ---------------------------------------------------------------------------
 constexpr int kConvKV = 4;     // widest d_conv of the vector kernels
-#ifndef MB200_CONV_FWD_TT
-#define MB200_CONV_FWD_TT 32
-#endif
-#ifndef MB200_CONV_UNR
-#define MB200_CONV_UNR 2
-#endif
-#ifndef MB200_CONV_BWD_VEC
-#define MB200_CONV_BWD_VEC 2
-#endif
-#ifndef MB200_CONV_FWD_BYTES
-#define MB200_CONV_FWD_BYTES 8
-#endif
-constexpr int kConvFwdTT = MB200_CONV_FWD_TT;  // timesteps per thread, forward
-constexpr int kConvUnr = MB200_CONV_UNR;        // steps of loads in flight per thread
+constexpr int kConvFwdTT = 32;      // timesteps per thread, forward
+constexpr int kConvUnr = 2;         // steps of loads in flight per thread
+constexpr int kConvFwdBytes = 8;    // bytes one forward thread moves per step
+// (a backward thread owns 2 channels with 16-bit storage, 4 with f32)
 
 template <typename Tact, int VEC>
 __device__ __forceinline__ void load_vec(const Tact* ptr, float* out) {
@@ -324,7 +316,7 @@ __device__ __forceinline__ void conv_load_taps(const ConvParams& p, int d, float
 
 template <typename Tact>
 __global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) {
-    constexpr int VEC = MB200_CONV_FWD_BYTES / sizeof(Tact), KV = kConvKV;
+    constexpr int VEC = kConvFwdBytes / sizeof(Tact), KV = kConvKV;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const int t0 = blockIdx.y * kConvFwdTT, b = blockIdx.z;
     if (d >= p.D) return;
@@ -375,7 +367,7 @@ __global__ void __launch_bounds__(64) conv1d_fwd_vec_kernel(const ConvParams p) 
 
 template <typename Tact>
 __global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) {
-    constexpr int VEC = (MB200_CONV_BWD_VEC == 8 && sizeof(Tact) == 2) ? 8 : (MB200_CONV_BWD_VEC == 2 && sizeof(Tact) == 2) ? 2 : 4, KV = kConvKV;
+    constexpr int VEC = sizeof(Tact) == 2 ? 2 : 4, KV = kConvKV;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const int chunk = blockIdx.y, t0 = chunk * kConvTT, b = blockIdx.z;
     if (d >= p.D) return;
@@ -551,6 +543,10 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_step(void* handle, void* stream,
     p.conv_state = a.conv_state; p.ssm_state = a.ssm_state;
     p.B = a.B; p.D = a.D; p.N = a.N; p.K = a.conv_w ? a.K : 0;
     p.delta_softplus = a.delta_softplus; p.z_mode = a.z_mode;
+    // f32 slices of a flat weight / state arena are only 4-byte aligned in general:
+    // the float4 path needs 16-byte bases (rows are then aligned since N % 4 == 0).
+    p.vec_state = (a.N % 4 == 0) && reinterpret_cast<uintptr_t>(a.a_neg) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(a.ssm_state) % 16 == 0;
     const long long n = static_cast<long long>(a.B) * a.D;
     const unsigned blocks = static_cast<unsigned>((n + 127) / 128);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -594,7 +590,7 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_fwd(void* handle, void* stream,
     dim3 grid((a.D + 127) / 128, chunks, a.B);
     const unsigned sb = static_cast<unsigned>((static_cast<long long>(a.B) * a.D + 127) / 128);
     const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
-    const int vec = static_cast<int>(MB200_CONV_FWD_BYTES / es);
+    const int vec = static_cast<int>(kConvFwdBytes / es);
     const bool use_vec = conv_vec_ok(a.K, a.D, vec, es, {a.x, a.u}, {a.ld_x, a.ld_u}) &&
                          reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
     dim3 vgrid((a.D / vec + 63) / 64, (a.T + kConvFwdTT - 1) / kConvFwdTT, a.B);
@@ -643,7 +639,7 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((a.D + 127) / 128, chunks, a.B);
     const size_t es = a.dtype == MAMBA_B200_F32 ? 4 : 2;
-    const int bvec = (MB200_CONV_BWD_VEC == 8 && es == 2) ? 8 : (MB200_CONV_BWD_VEC == 2 && es == 2) ? 2 : 4;
+    const int bvec = es == 2 ? 2 : 4;
     const bool use_vec = conv_vec_ok(a.K, a.D, bvec, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx}) &&
                          reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
     dim3 vgrid((a.D / bvec + 63) / 64, chunks, a.B);
@@ -679,18 +675,20 @@ constexpr int kMaxDevices = 64;
 // Device address of g_conv_bwd_scratch per device ordinal.  In host code the
 // symbol itself is only a stand-in; the address a kernel may dereference comes
 // from cudaGetSymbolAddress, asked once per device with that device current.
-static float* g_scratch_addr[kMaxDevices] = {nullptr};
+// Host threads may make their first call on a device at the same time: the slot is
+// an atomic, and two racing look-ups store the same address.
+static std::atomic<float*> g_scratch_addr[kMaxDevices];
 
 static int static_scratch_for_current_device(float** out, int* device) {
     if (cudaGetDevice(device) != cudaSuccess) return MAMBA_B200_ERR_CUDA;
     if (*device < 0 || *device >= kMaxDevices) return MAMBA_B200_ERR_DEVICE;
-    if (!g_scratch_addr[*device]) {
-        float* ptr = nullptr;
+    float* ptr = g_scratch_addr[*device].load(std::memory_order_acquire);
+    if (!ptr) {
         if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_conv_bwd_scratch) != cudaSuccess || !ptr)
             return MAMBA_B200_ERR_CUDA;
-        g_scratch_addr[*device] = ptr;
+        g_scratch_addr[*device].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_addr[*device];
+    *out = ptr;
     return MAMBA_B200_OK;
 }
 
@@ -715,6 +713,10 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd_static(void* handle, void* s
     int device = -1;
     int rc = static_scratch_for_current_device(&scratch, &device);
     if (rc) return fail(c, rc, "conv1d_bwd_static: cannot resolve the scratch address on device %d", device);
+    if (c && c->device != device)
+        return fail(c, MAMBA_B200_ERR_DEVICE,
+                    "conv1d_bwd_static: the handle belongs to device %d but device %d is current", c->device,
+                    device);
     a.workspace = scratch;
     a.workspace_bytes = mamba_b200_conv1d_bwd_static_max_bytes();
     // Every partial the reduction reads is written by this call's first kernel,

@@ -964,8 +964,7 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
         !a.d_adt || !a.d_dt || !a.d_trap || !a.dD || !a.workspace)
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: null required pointer");
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    static const bool cuda_cores_env = getenv("MAMBA_B200_M3_BWD_CUDA_CORES") != nullptr;
-    const bool tensor_core = m3_bwd_tc_shape(a.dtype, a.hd, a.N) && !cuda_cores_env && al16(a.x) && al16(a.K) &&
+    const bool tensor_core = m3_bwd_tc_shape(a.dtype, a.hd, a.N) && al16(a.x) && al16(a.K) &&
                              al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) && al16(a.dQ);
     size_t o_g, o_s, o_d, total;
     // a misaligned tensor-core-shaped call falls back to the CUDA-core kernel and its larger scratch

@@ -132,6 +132,7 @@ def lib() -> C.CDLL:
                 raise LibraryMissing(f"{_LIB} does not export {name}: rebuild it")
 
         vp = C.c_void_p
+        bind("mamba_b200_selftest_wait_timeout", [vp, vp, C.c_int])
         bind("mamba_b200_sscan_fwd", [vp, vp, C.POINTER(SscanFwdArgs)])
         bind("mamba_b200_sscan_bwd", [vp, vp, C.POINTER(SscanBwdArgs)])
         bind("mamba_b200_sscan_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)

@@ -116,3 +116,33 @@ def test_conv_then_scan_equals_fused_conv_scan(cuda_dev):
     y_split = mb.selective_scan_fwd(u, *args)
     torch.cuda.synchronize()
     assert rel_err(y_split.cpu().numpy(), y_fused.cpu().numpy()) <= 1e-6
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_decode_step_with_state_slices_that_are_only_4_byte_aligned(cuda_dev, dt):
+    """a_neg and ssm_state as slices of flat f32 arenas (the reference keeps weights and
+    state that way): bases 4 bytes off a 16-byte boundary take the scalar state path."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, D, N, K = 3, 40, 16, 4
+    q = quantised_inputs(B, 1, D, N, K, dt, seed=77, a_mode="random")
+    ssm0, cst0 = random_states(B, D, N, K, seed=78)
+    td = torch_dtype(dt)
+    d = lambda a, t_=None: to_dev(a, cuda_dev, t_)
+    arena_a = torch.zeros(D * N + 1, device=cuda_dev)
+    arena_h = torch.zeros(B * D * N + 1, device=cuda_dev)
+    a_neg = arena_a[1:].view(D, N)
+    ssm = arena_h[1:].view(B, D, N)
+    a_neg.copy_(d(q["a_neg"]))
+    ssm.copy_(d(ssm0))
+    assert a_neg.data_ptr() % 16 == 4 and ssm.data_ptr() % 16 == 4
+    cst = d(cst0)
+    y = mb.selective_scan_step(d(q["x"][:, 0], td), d(q["delta_raw"][:, 0], td), d(q["Bm"][:, 0], td),
+                               d(q["Cm"][:, 0], td), a_neg, d(q["Dp"]), ssm, d(q["z"][:, 0], td),
+                               conv_w=d(q["conv_w"]), conv_b=d(q["conv_b"]), conv_state=cst)
+    torch.cuda.synchronize()
+    ref = oracle.m1_step(q["x"][:, 0], q["delta_raw"][:, 0], q["Bm"][:, 0], q["Cm"][:, 0], q["z"][:, 0], q["a_neg"],
+                         q["Dp"], q["conv_w"], q["conv_b"], cst0, ssm0)
+    assert rel_err(y.float().cpu().numpy(), ref["y"]) <= TOL[dt]
+    assert rel_err(ssm.cpu().numpy(), ref["ssm_state"]) <= 1e-4

@@ -81,3 +81,37 @@ def test_static_scratch_entry_rejects_oversized_problems(cuda_dev):
     rc = lib.mamba_b200_conv1d_bwd_static(h.ptr, None, C.byref(a))
     assert rc == -2
     assert b"built-in" in lib.mamba_b200_last_error(h.ptr)
+
+
+def test_static_scratch_entry_without_a_handle_on_a_side_stream(cuda_dev):
+    """handle == NULL (failures by return code only) and a non-default stream,
+    checked against the CPU oracle rather than against the other entry point."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    import oracle
+    from mamba_rs_b200 import ffi
+    lib = ffi.lib()
+    lib.mamba_b200_conv1d_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(ffi.Conv1dArgs)]
+    ffi.default_handle(0)  # the first call on the device has been made before this one
+    B, T, D, K = 2, 130, 48, 4
+    rng = np.random.default_rng(9)
+    xn = rng.standard_normal((B, T, D)).astype(np.float32)
+    dun = rng.standard_normal((B, T, D)).astype(np.float32)
+    wn = rng.uniform(-0.8, 0.8, (D, K)).astype(np.float32)
+    bn = (0.1 * rng.standard_normal(D)).astype(np.float32)
+    sn = rng.standard_normal((B, D, K)).astype(np.float32)
+    t = lambda a: torch.from_numpy(a).to(cuda_dev)
+    x, d_u, w, b, st0 = t(xn), t(dun), t(wn), t(bn), t(sn)
+    d_x, dW, db = torch.empty_like(x), torch.zeros(D, K, device=cuda_dev), torch.zeros(D, device=cuda_dev)
+    side = torch.cuda.Stream(device=cuda_dev)
+    side.wait_stream(torch.cuda.current_stream(cuda_dev))
+    a = _args(ffi, mb, x, w, b, d_u, st0, d_x, dW, db, None)
+    rc = lib.mamba_b200_conv1d_bwd_static(None, C.c_void_p(side.cuda_stream), C.byref(a))
+    assert rc == 0
+    side.synchronize()
+    ref = oracle.conv1d_bwd(xn, wn, bn, dun, sn)
+    den = lambda r: max(np.abs(r).max(), 1e-30)
+    assert np.abs(d_x.cpu().numpy() - ref["d_x"]).max() / den(ref["d_x"]) <= 1e-4
+    assert np.abs(dW.cpu().numpy() - ref["dconv_w"]).max() / den(ref["dconv_w"]) <= 2e-4
+    assert np.abs(db.cpu().numpy() - ref["dconv_b"]).max() / den(ref["dconv_b"]) <= 2e-4
