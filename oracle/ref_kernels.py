@@ -62,6 +62,10 @@ class RefKernels:
                 vals.append(a.data_ptr())
                 types.append(C.c_void_p)
         stream = torch.cuda.current_stream().cuda_stream
+        if smem > 48 * 1024:  # beyond the default limit a kernel has to opt in (m3_dqkv at hd 32, N 64)
+            err, = self.drv.cuFuncSetAttribute(
+                fn, self.drv.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem)
+            assert err == self.drv.CUresult.CUDA_SUCCESS, err
         err, = self.drv.cuLaunchKernel(fn, grid[0], grid[1], grid[2], block, 1, 1, smem, stream,
                                        (tuple(vals), tuple(types)), 0)
         assert err == self.drv.CUresult.CUDA_SUCCESS, err
