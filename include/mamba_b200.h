@@ -10,7 +10,7 @@
  * boundary (src/mamba_ssm/gpu/buffers.rs:12-19,:142-147, forward_mixed.rs:150-155):
  *   - every pointer is a DEVICE pointer owned by the caller; nothing here
  *     allocates, frees or synchronises; launches are asynchronous on `stream`
- *     (a CUstream / cudaStream_t passed as void*) and are graph-capturable;
+ *     (a CUstream / cudaStream_t passed as void*);
  *   - activations are stored as f32 / f16 / bf16 (`dtype`), all arithmetic,
  *     recurrent state, a_neg, D, and every gradient accumulator is f32
  *     (kernels/mamba_ssm.cu:573-578, src/mamba_ssm/gpu/dtype.rs:12-28);
@@ -103,8 +103,15 @@ typedef struct mamba_b200_sscan_fwd_args {
     float* chunk_states; /* optional training save: [B, ceil(T/save_stride), D, N], the state
                             ENTERING each block of save_stride steps (replaces h_saved) */
     int save_stride;     /* 32 or 64 when chunk_states != NULL; 32 is the backward's fast setting */
+    void* workspace;     /* optional caller-owned scratch, 256-byte aligned, or NULL.  With it, a
+                            launch whose batch x channels cannot fill the GPU is cut along the
+                            sequence into up to 16 segments that run side by side (a first pass
+                            for the segments' leaving states, an exact carry, then the full pass);
+                            without it the sequence is always walked by one CTA per channel tile. */
+    long long workspace_bytes; /* >= mamba_b200_sscan_fwd_workspace_bytes(B,T,D,N) uses every segment */
 } mamba_b200_sscan_fwd_args;
 
+MAMBA_B200_API long long mamba_b200_sscan_fwd_workspace_bytes(int B, int T, int D, int N);
 MAMBA_B200_API int mamba_b200_sscan_fwd(void* handle, void* stream, const mamba_b200_sscan_fwd_args* args);
 
 /*

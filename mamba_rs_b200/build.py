@@ -36,14 +36,21 @@ def build(force: bool = False, verbose: bool = False, extra=()) -> str:
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if not f.endswith(".cu")]
+    headers.append(os.path.join(HERE, "..", "include", "mamba_b200.h"))
+    newest_header = max(os.path.getmtime(h) for h in headers)
     for src in sources():
         obj = os.path.join(HERE, "build", os.path.basename(src) + ".o")
+        objs.append(obj)
+        # an object newer than its source and every header is reused
+        if (not force and not extra and os.path.exists(obj)
+                and os.path.getmtime(obj) > max(os.path.getmtime(src), newest_header)):
+            continue
         cmd = [nvcc, *[f for f in NVCC_FLAGS if f != "--shared"], *extra, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
-        objs.append(obj)
     for src, p in procs:
         out, _ = p.communicate()
         if verbose or p.returncode:
@@ -55,5 +62,5 @@ def build(force: bool = False, verbose: bool = False, extra=()) -> str:
 
 
 if __name__ == "__main__":
-    build(force=True, verbose="-v" in sys.argv)
+    build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(LIB)

@@ -1,43 +1,81 @@
 // Mamba-1 fused selective-scan forward for sm_100a.
 // Host side of the fused forward: argument validation, TMA descriptors, variant
-// selection and launch.  The kernels live in m1_fwd_kernel.cuh.
-#include <stdlib.h>
-
+// selection, the time-segment plan and launch.  The kernels live in
+// m1_fwd_kernel.cuh.
 #include "m1_fwd_kernel.cuh"
 
 namespace mb200 {
+
+constexpr int kMaxSegments = 16;
 
 struct FwdTable {
     FwdVariant v[3][kMaxFwdVariants];
     int n[3];
 };
 
+// Built once, under the thread-safe initialisation of a function-local static.
 static const FwdTable& fwd_table() {
-    static FwdTable t;
-    static bool init = false;
-    if (!init) {
+    static const FwdTable table = [] {
+        FwdTable t;
         memset(&t, 0, sizeof(t));
-#ifndef MB200_FWD_BF16_ONLY
         t.n[MAMBA_B200_F32] = fwd_variants_f32(t.v[MAMBA_B200_F32]);
         t.n[MAMBA_B200_F16] = fwd_variants_f16(t.v[MAMBA_B200_F16]);
-#endif
         t.n[MAMBA_B200_BF16] = fwd_variants_bf16(t.v[MAMBA_B200_BF16]);
-        init = true;
-    }
-    return t;
+        return t;
+    }();
+    return table;
 }
 
 int m1_fwd_configure(Ctx* c) {
     const FwdTable& t = fwd_table();
     for (int dt = 0; dt < 3; ++dt)
         for (int i = 0; i < t.n[dt]; ++i)
-            for (int f = 0; f < 8; ++f)
+            for (int f = 0; f < 16; ++f)
                 if (t.v[dt][i].fn[f] && t.v[dt][i].smem <= 227 * 1024)
                     MB200_CUDA_CHECK(c, cudaFuncSetAttribute(
                                             reinterpret_cast<const void*>(t.v[dt][i].fn[f]),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(t.v[dt][i].smem)));
     return MAMBA_B200_OK;
+}
+
+// Segment hand-over: slot s of seg_states arrives holding the state segment s
+// leaves when started from zero (segment 0: from the real entering state) and
+// leaves holding the true state at the end of segment s, i.e. the one segment
+// s + 1 starts from.  A segment's decay is exp(a * sum of its deltas): the carry
+// costs one exp2 per state and segment.
+__global__ void sscan_seg_carry_kernel(float* seg_states, const float* seg_sumdl, const float* a_neg,
+                                       int B, int S, int D, int N) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(B) * D * N) return;
+    const int n = static_cast<int>(i % N);
+    const int d = static_cast<int>((i / N) % D);
+    const int b = static_cast<int>(i / (static_cast<long long>(N) * D));
+    const float a2 = a_neg[static_cast<long long>(d) * N + n] * kLog2e;
+    float run = seg_states[((static_cast<long long>(b) * S + 0) * D + d) * N + n];
+    for (int s = 1; s + 1 < S; ++s) {
+        const long long at = ((static_cast<long long>(b) * S + s) * D + d) * N + n;
+        const float sum = seg_sumdl[(static_cast<long long>(b) * S + s) * D + d];
+        run = fmaf(ex2(a2 * sum), run, seg_states[at]);
+        seg_states[at] = run;
+    }
+}
+
+static size_t fwd_ws_bytes(int B, int D, int N, int segs, size_t* o_sum, size_t* o_h0, size_t* o_c0) {
+    auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
+    size_t off = al(sizeof(float) * static_cast<size_t>(B) * segs * D * N);
+    *o_sum = off;
+    off += al(sizeof(float) * static_cast<size_t>(B) * segs * D);
+    *o_h0 = off;
+    off += al(sizeof(float) * static_cast<size_t>(B) * D * N);
+    *o_c0 = off;
+    off += al(sizeof(float) * static_cast<size_t>(B) * D * kKMax);
+    return off;
+}
+
+static bool overlaps(const void* a, size_t na, const void* b, size_t nb) {
+    const uintptr_t x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
+    return a && b && x < y + nb && y < x + na;
 }
 
 static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_args& a) {
@@ -61,6 +99,13 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     if (misaligned(a.x) || misaligned(a.delta) || misaligned(a.Bm) || misaligned(a.Cm) ||
         misaligned(a.y) || (a.z && misaligned(a.z)) || (a.u_out && misaligned(a.u_out)))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: pointer not aligned to its element size");
+    // With the conv fused, a chunk re-reads the rows of x just before it: y (or u_out)
+    // written over x would be read back as input.
+    const size_t span_x = (static_cast<size_t>(a.B) * a.T - 1) * a.ld_x * es + a.D * es;
+    if (a.conv_w && (overlaps(a.x, span_x, a.y, (static_cast<size_t>(a.B) * a.T - 1) * a.ld_y * es + a.D * es) ||
+                     (a.u_out && overlaps(a.x, span_x, a.u_out,
+                                          (static_cast<size_t>(a.B) * a.T - 1) * a.ld_u * es + a.D * es))))
+        return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: with the conv fused, y and u_out must not overlap x");
 
     const FwdTable& tab = fwd_table();
     const FwdVariant* vs = tab.v[a.dtype];
@@ -68,7 +113,7 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     for (int i = 0; i < tab.n[a.dtype]; ++i)
         if (vs[i].ns * vs[i].lpc >= a.N) { v = &vs[i]; break; }
     if (!v) return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_fwd: no variant for d_state %d", a.N);
-    if (a.chunk_states && (a.save_stride <= 0 || a.save_stride % v->tc != 0 || a.save_stride > 64))
+    if (a.chunk_states && (a.save_stride <= 0 || a.save_stride % 32 != 0 || a.save_stride > 64))
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: save_stride %d must be 32 or 64", a.save_stride);
 
     FwdParams p;
@@ -80,48 +125,72 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     p.a_neg = a.a_neg; p.Dp = a.Dp; p.conv_w = a.conv_w; p.conv_b = a.conv_b;
     p.conv_state = a.conv_w ? a.conv_state : nullptr;
     p.ssm_state = a.ssm_state; p.chunk_states = a.chunk_states;
+    p.conv_in = p.conv_state; p.ssm_in = p.ssm_state;
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.K = a.conv_w ? a.K : 0;
-    p.delta_softplus = a.delta_softplus; p.z_mode = a.z_mode;
+    p.z_mode = a.z_mode;
     p.save_stride = a.chunk_states ? a.save_stride : 1;
     p.status = c->d_status;
-    p.u_vec = (a.u_out && (a.ld_u % 2 == 0) && (reinterpret_cast<uintptr_t>(a.u_out) % (2 * es) == 0)) ? 1 : 0;
     unsigned m = 0;
-    // The y tile must not alias rows of other tensors the same CTA still reads
-    // through TMA; in-place use (y == x) is served by the plain-store path.
-    if (make_tmap_3d(c, &p.tm_x, a.dtype, a.x, a.ld_x, a.D, a.T, a.B, v->dt, v->tc)) m |= kTmaX;
+    const int xrows = a.conv_w ? v->tc + kHaloRows : v->tc;
+    if (make_tmap_3d(c, &p.tm_x, a.dtype, a.x, a.ld_x, a.D, a.T, a.B, v->dt, xrows)) m |= kTmaX;
     if (make_tmap_3d(c, &p.tm_dl, a.dtype, a.delta, a.ld_delta, a.D, a.T, a.B, v->dt, v->tc)) m |= kTmaDl;
     if (a.z_mode && make_tmap_3d(c, &p.tm_z, a.dtype, a.z, a.ld_z, a.D, a.T, a.B, v->dt, v->tc)) m |= kTmaZ;
-    if (!a.z_mode) m |= kTmaZ;  // nothing to load
     if (make_tmap_3d(c, &p.tm_b, a.dtype, a.Bm, a.ld_bc, a.N, a.T, a.B, a.N, v->tc)) m |= kTmaB;
     if (make_tmap_3d(c, &p.tm_c, a.dtype, a.Cm, a.ld_bc, a.N, a.T, a.B, a.N, v->tc)) m |= kTmaC;
-    if (make_tmap_3d(c, &p.tm_y, a.dtype, a.y, a.ld_y, a.D, a.T, a.B, v->dt, v->tc)) m |= kTmaY;
     p.tma_mask = m;
 
     const int flags = (a.delta_softplus ? 1 : 0) | (a.z_mode ? 2 : 0) | (a.conv_w ? 4 : 0);
     FwdKernelFn fn = v->fn[flags];
-    if (!fn || v->smem > 227 * 1024)
+    FwdKernelFn fn_state = v->fn[8 | (flags & 5)];
+    if (!fn || !fn_state || v->smem > 227 * 1024)
         return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_fwd: no kernel for dtype %d flags %d d_state %d",
                     a.dtype, flags, a.N);
-    // Time segments: when batch x channel tiles cannot even give every warp
-    // scheduler one warp (small-batch prefill), split the sequence; each extra
-    // segment replays the earlier ones for its entering state (about half the
-    // cost of a full chunk), so at most 3 segments.  Measured on B200: no gain
-    // once the schedulers hold 2-3 warps each (the kernel is then bound by
-    // instruction throughput, and replay only adds instructions).
-    const long long tiles = static_cast<long long>((a.D + v->dt - 1) / v->dt) * a.B;
-    const long long warps = tiles * (v->threads / 32);
+
+    // Time segments.  When batch x channel tiles leave warp schedulers idle
+    // (small-batch prefill) and the caller lent a workspace, the sequence is cut
+    // into S segments that run side by side: a first launch walks segments
+    // 0 .. S-2 for their leaving states only (segment s > 0 from a zero state,
+    // keeping the sum of its deltas), a small kernel chains them into the true
+    // entering states, and the second launch runs every segment in full.
+    const int tiles = (a.D + v->dt - 1) / v->dt;
+    const long long warps = static_cast<long long>(tiles) * a.B * (v->threads / 32 - 1);
     const int nchunks = (a.T + v->tc - 1) / v->tc;
     int segs = 1;
-    const char* env = getenv("MAMBA_B200_FWD_SEGMENTS");
-    if (env && atoi(env) > 0) segs = atoi(env);
-    else {
-        const long long want = 4ll * c->sm_count;  // one warp per scheduler at least
-        while (segs < 3 && warps * segs < want && nchunks >= 8 * (segs + 1)) ++segs;
+    if (a.workspace && a.workspace_bytes > 0) {
+        const long long want = 8ll * c->sm_count;  // two warps per scheduler
+        while (segs < kMaxSegments && warps * segs < want && nchunks / (segs * 2) >= 4) segs *= 2;
+        size_t o1, o2, o3;
+        while (segs > 1 && fwd_ws_bytes(a.B, a.D, a.N, segs, &o1, &o2, &o3) > static_cast<size_t>(a.workspace_bytes))
+            segs /= 2;
+        if (segs > 1 && reinterpret_cast<uintptr_t>(a.workspace) % 256)
+            return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: workspace must be 256-byte aligned");
     }
-    if (segs > nchunks) segs = nchunks > 0 ? nchunks : 1;
-    p.seg_chunks = segs > 1 ? (nchunks + segs - 1) / segs : 0;
-    if (segs > 1) segs = (nchunks + p.seg_chunks - 1) / p.seg_chunks;
-    dim3 grid((a.D + v->dt - 1) / v->dt, a.B, segs);
+    dim3 grid(tiles, a.B, 1);
+    if (segs > 1) {
+        p.seg_chunks = (nchunks + segs - 1) / segs;
+        segs = (nchunks + p.seg_chunks - 1) / p.seg_chunks;
+    }
+    if (segs > 1) {
+        size_t o_sum, o_h0, o_c0;
+        fwd_ws_bytes(a.B, a.D, a.N, segs, &o_sum, &o_h0, &o_c0);
+        unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+        p.seg_states = reinterpret_cast<float*>(ws);
+        p.seg_sumdl = reinterpret_cast<float*>(ws + o_sum);
+        grid.z = segs;
+        FwdParams p1 = p;  // state-only pass: also keeps the entering states for the second pass
+        p1.ssm_copy = reinterpret_cast<float*>(ws + o_h0);
+        p1.conv_copy = p.K ? reinterpret_cast<float*>(ws + o_c0) : nullptr;
+        fn_state<<<grid, v->threads, v->smem, stream>>>(p1);
+        MB200_CUDA_CHECK(c, cudaGetLastError());
+        const long long n = static_cast<long long>(a.B) * a.D * a.N;
+        sscan_seg_carry_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+            p.seg_states, p.seg_sumdl, a.a_neg, a.B, segs, a.D, a.N);
+        MB200_CUDA_CHECK(c, cudaGetLastError());
+        // segment 0 of the second pass reads the copies: the last segment overwrites the
+        // caller's state arrays while other segments may still be starting
+        p.ssm_in = p1.ssm_copy;
+        p.conv_in = p1.conv_copy;
+    }
     fn<<<grid, v->threads, v->smem, stream>>>(p);
     MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;
@@ -130,6 +199,13 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
 }  // namespace mb200
 
 using namespace mb200;
+
+extern "C" MAMBA_B200_API long long mamba_b200_sscan_fwd_workspace_bytes(int B, int T, int D, int N) {
+    (void)T;
+    if (B <= 0 || D <= 0 || N <= 0 || N > 256) return 0;
+    size_t o1, o2, o3;
+    return static_cast<long long>(fwd_ws_bytes(B, D, N, kMaxSegments, &o1, &o2, &o3));
+}
 
 extern "C" MAMBA_B200_API int mamba_b200_sscan_fwd(void* handle, void* stream, const mamba_b200_sscan_fwd_args* args) {
     Ctx* c = static_cast<Ctx*>(handle);

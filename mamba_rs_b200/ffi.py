@@ -33,6 +33,7 @@ class SscanFwdArgs(C.Structure):
         ("y", C.c_void_p), ("ld_y", C.c_longlong),
         ("u_out", C.c_void_p), ("ld_u", C.c_longlong),
         ("chunk_states", C.c_void_p), ("save_stride", C.c_int),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong),
     ]
 
 
@@ -134,6 +135,7 @@ def lib() -> C.CDLL:
         vp = C.c_void_p
         bind("mamba_b200_selftest_wait_timeout", [vp, vp, C.c_int])
         bind("mamba_b200_sscan_fwd", [vp, vp, C.POINTER(SscanFwdArgs)])
+        bind("mamba_b200_sscan_fwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
         bind("mamba_b200_sscan_bwd", [vp, vp, C.POINTER(SscanBwdArgs)])
         bind("mamba_b200_sscan_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
         bind("mamba_b200_sscan_step", [vp, vp, C.POINTER(SscanStepArgs)])

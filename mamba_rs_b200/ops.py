@@ -15,7 +15,8 @@ import torch
 
 from . import ffi
 
-__all__ = ["selective_scan_fwd", "selective_scan_bwd", "selective_scan_bwd_workspace_bytes",
+__all__ = ["selective_scan_fwd", "selective_scan_fwd_workspace_bytes", "selective_scan_bwd",
+           "selective_scan_bwd_workspace_bytes",
            "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
 
 
@@ -53,11 +54,13 @@ def _stream(dev):
 def selective_scan_fwd(x, delta, Bm, Cm, a_neg, Dp, z=None, *, z_mode=None,
                        delta_softplus=True, conv_w=None, conv_b=None, conv_state=None,
                        ssm_state=None, y=None, u_out=None, chunk_states=None, save_stride=0,
-                       handle=None):
+                       workspace=None, handle=None):
     """Fused forward ``[conv1d+SiLU] -> softplus -> scan -> +D*u -> *SiLU(z)``.
 
     x, delta, z: [B,T,D]; Bm, Cm: [B,T,N]; a_neg [D,N] f32; Dp [D] f32.
     conv_state [B,D,K] / ssm_state [B,D,N] f32 are updated in place.
+    workspace: optional uint8 scratch of selective_scan_fwd_workspace_bytes(...)
+    bytes; with it a small batch is cut into time segments that run side by side.
     Returns y [B,T,D] in the storage dtype of x."""
     _require_cuda(x, delta, Bm, Cm, a_neg, Dp, z, conv_w, conv_b, conv_state, ssm_state, y, u_out)
     Bsz, T, D = delta.shape
@@ -91,6 +94,9 @@ def selective_scan_fwd(x, delta, Bm, Cm, a_neg, Dp, z=None, *, z_mode=None,
     a.y, a.ld_y = _ptr(y), _rows(y, "y")
     a.u_out, a.ld_u = _ptr(u_out), (_rows(u_out, "u_out") if u_out is not None else 0)
     a.chunk_states, a.save_stride = _ptr(chunk_states), int(save_stride)
+    if workspace is not None:
+        _require_cuda(workspace)
+        a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel() * workspace.element_size()
     with torch.cuda.device(dev):
         rc = ffi.lib().mamba_b200_sscan_fwd(h.ptr, _stream(dev), C.byref(a))
     h.check(rc, "mamba_b200_sscan_fwd")
@@ -116,6 +122,11 @@ def ssm_parallel_scan_fwd_nosave(h_state, y_out, delta, u, Bm, Cm, a_neg, Dp, *,
                 C.c_int(T), C.c_int(D), C.c_int(N))
     hd.check(rc, "mamba_b200_ssm_scan_fwd_nosave")
     return y_out
+
+
+def selective_scan_fwd_workspace_bytes(B, T, D, N) -> int:
+    """Bytes of the optional forward scratch (segment hand-over states)."""
+    return int(ffi.lib().mamba_b200_sscan_fwd_workspace_bytes(B, T, D, N))
 
 
 def selective_scan_bwd_workspace_bytes(B, T, D, N) -> int:

@@ -42,6 +42,7 @@ SHAPES = [
     (2, 40, 64, 16, 0), (2, 100, 48, 16, 4), (1, 1, 32, 16, 4), (1, 3, 5, 16, 4), (1, 15, 33, 16, 4),
     (1, 16, 64, 16, 0), (1, 17, 130, 16, 4), (3, 65, 7, 4, 3), (1, 33, 20, 8, 4), (1, 50, 12, 12, 2),
     (1, 50, 12, 64, 4), (1, 20, 6, 32, 4), (1, 9, 3, 128, 2), (2, 300, 256, 16, 4), (1, 257, 64, 16, 4),
+    (1, 40, 2, 256, 0), (1, 70, 3, 200, 4),
 ]
 
 
@@ -260,3 +261,47 @@ def test_full_size_linearity_and_split_at_config2(cuda_dev):
                               inp["a_neg"][dsel], inp["Dp"][dsel])
     assert rel_err(f(y1)[..., dsel], ref["y"]) <= TOL["bf16"]
     assert rel_err(h[bsel, dsel].cpu().numpy(), ref["ssm_state"][0]) <= 1e-4
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 2048, 40, 16, 4), (2, 1100, 24, 16, 0), (1, 4100, 8, 8, 3), (1, 1500, 16, 64, 4)],
+                         ids=lambda s: "B%dT%dD%dN%dK%d" % s)
+def test_time_segments_with_exact_carry_match_oracle(cuda_dev, shape, dt):
+    """A small batch with a lent workspace is cut into time segments that run side by
+    side (state-only pass, carry, full pass).  Fused conv, conv / ssm state updated in
+    place, training saves: everything must match the one-piece oracle."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, T, D, N, K = shape
+    q = quantised_inputs(B, T, D, N, K, dt, seed=T + D, a_mode="random")
+    ssm0, cst0 = random_states(B, D, N, K, seed=T)
+    ref = oracle.m1_fused_fwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"],
+                              q.get("conv_w"), q.get("conv_b"), cst0, ssm0, want_h=True)
+    td = torch_dtype(dt)
+    d = lambda a_, t_=None: to_dev(a_, cuda_dev, t_)
+    ssm = d(ssm0)
+    cst = d(cst0) if K else None
+    S = 32
+    cs = torch.empty(B, (T + S - 1) // S, D, N, device=cuda_dev)
+    ws = torch.empty(mb.selective_scan_fwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=cuda_dev)
+    y = mb.selective_scan_fwd(d(q["x"], td), d(q["delta_raw"], td), d(q["Bm"], td), d(q["Cm"], td), d(q["a_neg"]),
+                              d(q["Dp"]), d(q["z"], td), conv_w=d(q.get("conv_w")), conv_b=d(q.get("conv_b")),
+                              conv_state=cst, ssm_state=ssm, chunk_states=cs, save_stride=S, workspace=ws)
+    torch.cuda.synchronize()
+    mb.ffi.default_handle(0).check_status()
+    assert rel_err(y.float().cpu().numpy(), ref["y"]) <= TOL[dt]
+    assert rel_err(ssm.cpu().numpy(), ref["ssm_state"]) <= 1e-4
+    if K:
+        np.testing.assert_array_equal(cst.cpu().numpy(), ref["conv_state"])
+    got = cs.cpu().numpy()
+    for k in range(got.shape[1]):
+        assert rel_err(got[:, k], ref["h_all"][:, k * S]) <= 1e-4, k
+    # and the same call without a workspace (one segment) gives the same numbers
+    ssm1 = d(ssm0)
+    y1 = mb.selective_scan_fwd(d(q["x"], td), d(q["delta_raw"], td), d(q["Bm"], td), d(q["Cm"], td), d(q["a_neg"]),
+                               d(q["Dp"]), d(q["z"], td), conv_w=d(q.get("conv_w")), conv_b=d(q.get("conv_b")),
+                               conv_state=d(cst0) if K else None, ssm_state=ssm1)
+    torch.cuda.synchronize()
+    assert rel_err(y.float().cpu().numpy(), y1.float().cpu().numpy()) <= TOL[dt]
+    assert rel_err(ssm.cpu().numpy(), ssm1.cpu().numpy()) <= 1e-4
