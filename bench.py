@@ -2,6 +2,7 @@
 """Benchmark of the selective-scan hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --op NAME [--batch B] ...      one operator, one JSON line
 
 A step is one pass of the fused Mamba-1 selective-scan forward over one batch
 of synthetic input at the standalone-op configuration (batch 16 per GPU,
@@ -19,15 +20,22 @@ path.  Rank 0 prints one JSON line.
             the launching stream) against the measured HBM copy peak
   cpu_baseline: the CPU restatement of the reference's CPU path timed on the
             host cores of this box on a bounded sample of the same workload
-  backward: (1 GPU) the fused BPTT backward of the same workload, timed after
-            the headline region: ms, algorithmic GB/s, fraction of the HBM peak
+  extra   : (1 GPU) every other operator of the path, timed after the headline
+            region with CUDA events: scan forward with a trained-like a_neg,
+            scan backward, conv1d forward / backward, the Mamba-3 SSD forward /
+            backward, the decode loop (24 layers x 128 steps), small-batch
+            prefill with time segments
+            (N GPUs) the one collective of the design: the bucketed gradient
+            all-reduce, alone and overlapped with the scan backward
 
---impl reference times that CPU path alone (the reference is Rust and cannot
-be built without cargo; its CPU algorithm is restated in oracle/).
+--impl reference times the reference's CPU algorithm alone (the reference is
+Rust and cannot be built without cargo; its algorithm is restated in oracle/),
+on every host core, whatever thread count the launcher exported.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -43,6 +51,8 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(B=16, T=2048, D=1536, N=16, dtype="bf16")
 METRIC = "selective_scan_fwd_algorithmic_GBps"
 FALLBACK_HBM_GBS = 6650.0
+OPS = ["sscan_fwd", "sscan_fwd_random_a", "sscan_fwd_unfused", "sscan_fwd_small_batch", "sscan_bwd", "conv1d_fwd",
+       "conv1d_bwd", "sscan_step", "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd"]
 
 
 def measured_peaks():
@@ -100,16 +110,43 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload_name():
+    w = WORKLOAD
+    return (f"mamba1_selective_scan_fwd B={w['B']}/gpu D={w['D']} N={w['N']} L={w['T']} {w['dtype']} "
+            "storage, softplus(delta) + SiLU(z) gate + D skip fused")
+
+
+def config_block(world):
+    """The `config` object both arms print (same keys, same values for the same launch)."""
+    w = WORKLOAD
+    by = algorithmic_bytes(w)
+    return {"workload": workload_name(), "storage_dtype": "bf16", "accum_dtype": "f32",
+            "global_batch": world * w["B"], "seq_len": w["T"],
+            "parallelism": f"batch-sharded x{world}, no collective on the scan",
+            "l2": (f"inputs+outputs per step ({by / 1e6:.0f} MB) exceed the 126 MB L2" if by > 126e6 else
+                   f"inputs+outputs per step ({by / 1e6:.0f} MB) fit the 126 MB L2: not a valid bench size"),
+            "a_neg": "S4D-real -(n+1) (the reference's init): arithmetic-progression decay path"}
+
+
 def algorithmic_bytes(w):
     from mamba_rs_b200 import synth
     return synth.m1_fwd_algorithmic_bytes(w["B"], w["T"], w["D"], w["N"], 2, K=0, z=True)
 
 
-def cpu_leg(sample_B, sample_D, repeats=5):
+def host_threads():
+    """Every core this process may run on, whatever OMP_NUM_THREADS the launcher set."""
+    try:
+        os.sched_setaffinity(0, range(os.cpu_count() or 1))  # torchrun may have narrowed it
+    except Exception:
+        pass
+    import oracle
+    return oracle.set_num_threads()
+
+
+def cpu_scan_leg(sample_B, sample_D, repeats=5):
     """Times the oracle's fused forward (the reference's CPU algorithm, OpenMP over
-    samples x 8-channel blocks as PrefillMode::Parallel does) on a bounded
-    sample: `sample_B` sequences x `sample_D` channels of the workload, full
-    length.  Returns (algorithmic GB/s, threads, seconds)."""
+    samples x 8-channel blocks as PrefillMode::Parallel does) on `sample_B` sequences
+    x `sample_D` channels of the workload, full length.  Returns (GB/s, seconds)."""
     import oracle
     from mamba_rs_b200 import synth
     w = WORKLOAD
@@ -123,20 +160,39 @@ def cpu_leg(sample_B, sample_D, repeats=5):
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     by = synth.m1_fwd_algorithmic_bytes(sample_B, w["T"], sample_D, w["N"], 2, K=0, z=True)
-    return by / best / 1e9, oracle.num_threads(), best
+    return by / best / 1e9, best
+
+
+def cpu_prefill_leg(repeats=3):
+    """The named CPU baseline: backbone forward_prefill of the reference's small model
+    (d_model 128, 2 layers, d_inner 256, d_state 16, d_conv 4, dt_rank 8; batch 4 x 512,
+    weights seed 42, inputs N(0,1) seed 7), restated with its scalar-order GEMM, one
+    OpenMP task per sample.  Returns tokens/s and seconds per pass."""
+    import oracle
+    cfg = oracle.m1_config(d_model=128, n_layers=2, d_state=16, d_conv=4, expand=2, dt_rank=8, input_dim=128)
+    w = oracle.m1_weights_init(cfg, 42)
+    inp = np.random.default_rng(7).standard_normal((4, 512, 128)).astype(np.float32)
+    best = None
+    for _ in range(repeats + 1):
+        t0 = time.perf_counter()
+        r = oracle.m1_prefill_batch(cfg, w, inp)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return 4 * 512 / best, best, int(r["threads"])
 
 
 def run_reference(args):
     """Reference arm: the reference's own CPU algorithm for the path (restated in
-    oracle/, all host threads), each step a bounded sample of the workload."""
+    oracle/, all host threads), each step the full workload of one GPU."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_B, sample_D = WORKLOAD["B"], WORKLOAD["D"]
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    cores = host_threads()
     import oracle
     from mamba_rs_b200 import synth
     w = WORKLOAD
-    inp = synth.m1_scan_inputs(sample_B, w["T"], sample_D, w["N"], 0, seed=0, a_mode="s4d")
+    inp = synth.m1_scan_inputs(w["B"], w["T"], w["D"], w["N"], 0, seed=0, a_mode="s4d")
     q = {k: synth.round_to(v, "bf16") if k in ("x", "z", "delta_raw", "Bm", "Cm") else v
          for k, v in inp.items()}
     call = lambda: oracle.m1_fused_fwd(q["x"], q["delta_raw"], q["Bm"], q["Cm"], q["z"], q["a_neg"], q["Dp"])
@@ -146,24 +202,278 @@ def run_reference(args):
     for _ in range(args.steps):
         call()
     dt = (time.perf_counter() - t0) / args.steps
-    by = synth.m1_fwd_algorithmic_bytes(sample_B, w["T"], sample_D, w["N"], 2, K=0, z=True)
+    by = algorithmic_bytes(w)
     val = by / dt / 1e9
-    sample = f"the full workload per step ({sample_B} sequences x {sample_D} channels x L={w['T']})"
+    sample = (f"one GPU's workload per step ({w['B']} sequences x {w['D']} channels x L={w['T']}); the CPU "
+              "runs one such shard whatever the number of GPUs")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(), "storage": "bf16-rounded inputs, f32 arithmetic"},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
-                         "sample": sample},
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "storage_dtype": "bf16", "data": "synthetic",
+        "config": config_block(world),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                         "note": "the reference's Rust build is unavailable on this box (no cargo); this is "
+                                 "its CPU algorithm restated in C"},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def workload_name():
-    w = WORKLOAD
-    return (f"mamba1_selective_scan_fwd B={w['B']}/gpu D={w['D']} N={w['N']} L={w['T']} {w['dtype']} "
-            "storage, softplus(delta) + SiLU(z) gate + D skip fused")
+# --------------------------------------------------------------------------------------
+# one operator at a time (also the `extra` block of the headline line)
+# --------------------------------------------------------------------------------------
+
+def time_call(fn, steps, warmup):
+    import torch
+    for _ in range(max(warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def op_case(name, dev, batch=0, save_stride=32, heads=32, headdim=64, dstate=128, sequential=False):
+    """Builds one operator's seeded inputs on `dev`.  Returns (callable, algorithmic bytes of
+    one call, config dict)."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    from mamba_rs_b200 import synth
+    bf = torch.bfloat16
+    t = lambda a, d=None: torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(d or torch.float32)
+    e = 2
+    if name.startswith("m3_"):
+        B, T, nh, hd, N = batch or 8, 4096, heads, headdim, dstate
+        i = synth.m3_ssd_inputs(B, T, nh, hd, N, seed=0)
+        a = [t(i[k], bf if k in ("x", "K", "Q") else None) for k in ("x", "K", "Q", "dt", "trap", "adt", "Dh")]
+        cfg = dict(B=B, T=T, nh=nh, hd=hd, N=N, storage="bf16")
+        if name == "m3_ssd_fwd":
+            y = torch.empty_like(a[0])
+            ssm = torch.zeros(B, nh, hd, N, device=dev)
+            by = synth.m3_fwd_algorithmic_bytes(B, T, nh, hd, N, e)
+            return (lambda: mb.m3_ssd_fwd(*a, ssm_state=ssm, y=y, force_sequential=sequential)), by, cfg
+        dy = torch.randn(B, T, nh * hd, device=dev).to(bf)
+        ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes_for(2, B, T, nh, hd, N),
+                         dtype=torch.uint8, device=dev)
+        # x, K, Q, dy read; dx written; dK, dQ f32; five [B,T,nh] f32 vectors
+        by = (3 * e * B * T * nh * hd + 2 * e * B * T * nh * N + 2 * 4 * B * T * nh * N + 6 * 4 * B * T * nh)
+        return (lambda: mb.m3_ssd_bwd(*a, dy, workspace=ws)), by, cfg
+
+    small = name == "sscan_fwd_small_batch"
+    B = batch or (8 if name in ("sscan_step", "decode_loop") else (1 if small else 16))
+    T, D, N, K = (8192 if small else 2048), 1536, 16, 4
+    a_mode = "random" if name == "sscan_fwd_random_a" else "s4d"
+    inp = synth.m1_scan_inputs(B, 2 if name in ("sscan_step", "decode_loop") else T, D, N, K, seed=0, a_mode=a_mode)
+    a_neg, Dp, cw, cb = t(inp["a_neg"]), t(inp["Dp"]), t(inp["conv_w"]), t(inp["conv_b"])
+    cfg = dict(B=B, T=T, D=D, N=N, storage="bf16", a_neg=a_mode)
+    if name in ("sscan_step", "decode_loop"):
+        cfg.pop("T")
+        cfg["K"] = K
+        L = 24 if name == "decode_loop" else 1
+        STEPS = 128 if name == "decode_loop" else 1
+        cfg.update(layers=L, steps=STEPS)
+        xs, ds, zs = [torch.randn(B, D, device=dev).to(bf) for _ in range(3)]
+        bs, cs2 = [torch.randn(B, N, device=dev).to(bf) for _ in range(2)]
+        ssm = [torch.zeros(B, D, N, device=dev) for _ in range(L)]
+        cst = [torch.zeros(B, D, K, device=dev) for _ in range(L)]
+        ys = torch.empty(B, D, device=dev, dtype=bf)
+        by = L * STEPS * (2 * 4 * B * D * N + 2 * 4 * B * D * K + 4 * e * B * D)
+
+        def loop():
+            for _ in range(STEPS):
+                for l in range(L):
+                    mb.selective_scan_step(xs, ds, bs, cs2, a_neg, Dp, ssm[l], zs, conv_w=cw, conv_b=cb,
+                                           conv_state=cst[l], y=ys)
+        if name == "sscan_step":
+            return loop, by, cfg
+        # the decode loop is launch-bound: capture the 24 x 128 launches once, replay the graph
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            loop()  # every first call (handle set-up) happens before the capture
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            loop()
+        cfg["cuda_graph"] = True
+        cfg["tokens"] = B * STEPS
+        return graph.replay, by, cfg
+
+    x, dl, Bm, Cm, z = [t(inp[k], bf) for k in ("x", "delta_raw", "Bm", "Cm", "z")]
+    if name in ("sscan_fwd", "sscan_fwd_random_a", "sscan_fwd_small_batch"):
+        y = torch.empty_like(x)
+        ssm = torch.zeros(B, D, N, device=dev)
+        ws = None
+        if small:
+            ws = torch.empty(mb.selective_scan_fwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=dev)
+            cfg["time_segments"] = "exact carry, workspace lent"
+        by = synth.m1_fwd_algorithmic_bytes(B, T, D, N, e)
+        return (lambda: mb.selective_scan_fwd(x, dl, Bm, Cm, a_neg, Dp, z, ssm_state=ssm, y=y, workspace=ws)), by, cfg
+    if name == "sscan_fwd_unfused":
+        y = torch.empty_like(x)
+        ssm = torch.zeros(B, D, N, device=dev)
+        dsp = torch.nn.functional.softplus(dl.float()).to(bf)
+        by = synth.m1_fwd_algorithmic_bytes(B, T, D, N, e, z=False)
+        return (lambda: mb.ssm_parallel_scan_fwd_nosave(ssm, y, dsp, x, Bm, Cm, a_neg, Dp)), by, cfg
+    if name == "sscan_bwd":
+        S = save_stride
+        cfg["save_stride"] = S
+        cs = torch.empty(B, (T + S - 1) // S, D, N, device=dev)
+        mb.selective_scan_fwd(x, dl, Bm, Cm, a_neg, Dp, z, chunk_states=cs, save_stride=S)
+        dy = torch.randn(B, T, D, device=dev).to(bf)
+        ws = torch.empty(mb.selective_scan_bwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=dev)
+        by = 7 * e * B * T * D + 2 * e * B * T * N + 2 * 4 * B * T * N + 4 * B * ((T + S - 1) // S) * D * N
+        return (lambda: mb.selective_scan_bwd(x, dl, Bm, Cm, a_neg, Dp, dy, cs, S, z, workspace=ws)), by, cfg
+    cfg["K"] = K
+    if name == "conv1d_fwd":
+        u = torch.empty_like(x)
+        return (lambda: mb.conv1d_fwd(x, cw, cb, None, u)), 2 * e * B * T * D, cfg
+    if name == "conv1d_bwd":
+        dy = torch.randn(B, T, D, device=dev).to(bf)
+        ws = torch.empty(int(mb.ffi.lib().mamba_b200_conv1d_bwd_workspace_bytes(B, T, D, K)), dtype=torch.uint8,
+                         device=dev)
+        return (lambda: mb.conv1d_bwd(x, cw, cb, dy, None, workspace=ws)), 3 * e * B * T * D, cfg
+    raise ValueError(name)
+
+
+def measure_op(name, dev, steps=10, warmup=3, **kw):
+    import torch
+
+    import mamba_rs_b200 as mb
+    fn, by, cfg = op_case(name, dev, **kw)
+    ms = time_call(fn, steps, warmup)
+    mb.ffi.default_handle(dev.index or 0).check_status()
+    peak, src = measured_peaks()
+    gbs = by / (ms * 1e-3) / 1e9
+    out = {"op": name, "config": cfg, "ms": ms, "steps": steps, "algorithmic_bytes": by, "GBps": gbs,
+           "frac_of_hbm_peak": gbs / peak, "peak_source": src}
+    if "tokens" in cfg:
+        out["tokens_per_s"] = cfg["tokens"] / (ms * 1e-3)
+    del fn
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_op(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the library has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    out = measure_op(args.op, dev, steps=args.steps if args.steps != 100 else 10, warmup=max(args.warmup, 3),
+                     batch=args.batch, save_stride=args.save_stride, heads=args.heads, headdim=args.headdim,
+                     dstate=args.dstate, sequential=args.sequential)
+    out["note"] = "time per call through the Python operator, including its launch overhead"
+    print(json.dumps(out))
+
+
+def collective_extra(dev, world, rank):
+    """The one collective of the design, measured: all-reduce (sum) of a flat f32
+    gradient arena, bucketed per layer, alone and issued on a side stream while the scan
+    backward of the following layers runs (what a trainer does between backward and
+    optimiser).  8 layers of the 2.8b shape (d_inner 5120: 43.3 M parameters per layer
+    -> 173 MB per bucket) stand for its 64; the per-GPU shard is batch 2 x 8192."""
+    import torch
+    import torch.distributed as dist
+
+    import mamba_rs_b200 as mb
+    from mamba_rs_b200 import parallel, synth
+    L, per_layer = 8, 43_300_000
+    B, T, D, N, S = 2, 8192, 5120, 16, 32
+    bf = torch.bfloat16
+    arena = torch.zeros(L * per_layer, device=dev)
+    bounds = [(l * per_layer, (l + 1) * per_layer) for l in range(L)]
+    par = synth.m1_scan_inputs(1, 1, D, N, 0, seed=rank, a_mode="random")
+    a_neg = torch.from_numpy(par["a_neg"]).to(dev)
+    Dp = torch.from_numpy(par["Dp"]).to(dev)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    x, z, dy = rn(B, T, D).to(bf), rn(B, T, D).to(bf), rn(B, T, D).to(bf)
+    dl = (0.5 * rn(B, T, D) - 4.0).to(bf)
+    Bm, Cm = rn(B, T, N).to(bf), rn(B, T, N).to(bf)
+    cs = torch.empty(B, T // S, D, N, device=dev)
+    ws = torch.empty(mb.selective_scan_bwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=dev)
+    mb.selective_scan_fwd(x, dl, Bm, Cm, a_neg, Dp, z, chunk_states=cs, save_stride=S)
+    dA, dD = torch.zeros(D, N, device=dev), torch.zeros(D, device=dev)
+    bwd = lambda: mb.selective_scan_bwd(x, dl, Bm, Cm, a_neg, Dp, dy, cs, S, z, dA_log=dA, dD=dD, workspace=ws)
+
+    def step(overlap, compute=True, reduce=True):
+        red = parallel.BucketedGradReducer(arena, bounds)
+        for l in reversed(range(L)):
+            if compute:
+                bwd()
+            if reduce and overlap:
+                red.bucket_ready(l)
+        if reduce and not overlap:
+            for l in reversed(range(L)):
+                red.bucket_ready(l)
+        red.finish()
+
+    def timed(**kw):
+        for _ in range(2):
+            step(**kw)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            step(**kw)
+        e1.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt)
+
+    ms_bwd = timed(overlap=False, reduce=False)
+    ms_red = timed(overlap=False, compute=False)
+    ms_serial = timed(overlap=False)
+    ms_overlap = timed(overlap=True)
+    bytes_ = arena.numel() * 4
+    return {"collective": "all-reduce (sum) of the flat f32 gradient arena, one bucket per layer",
+            "layers": L, "bucket_bytes": per_layer * 4, "arena_bytes": bytes_,
+            "shard": f"B={B} T={T} D={D} N={N} bf16 per GPU", "ms_backward_only": ms_bwd, "ms_allreduce_only": ms_red,
+            "ms_backward_then_allreduce": ms_serial, "ms_overlapped": ms_overlap,
+            "bus_GBps_per_gpu": 2 * (world - 1) / world * bytes_ / (ms_red * 1e-3) / 1e9,
+            "nvlink_peer_copy_GBps_reference": 770.0,
+            "hidden_fraction": max(0.0, min(1.0, (ms_serial - ms_overlap) / max(ms_red, 1e-9)))}
+
+
+def bind_to_gpu_numa_node(local):
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, so that the
+    pinned staging buffers allocated afterwards are local to that node."""
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(local)
+        bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:
+        return None
+
+
+def ncu_traffic_bytes():
+    """dram read+write bytes of one launch of the dominant kernel from the ncu capture
+    summarised under profiles/: None when the kernel source has changed since."""
+    p = os.path.join(ROOT, "profiles", "sscan_fwd_traffic.txt")
+    try:
+        kv = dict(line.strip().split("=", 1) for line in open(p) if "=" in line)
+        src = open(os.path.join(ROOT, "mamba_rs_b200", "csrc", "m1_fwd_kernel.cuh"), "rb").read()
+        if kv.get("kernel_source_sha1") != hashlib.sha1(src).hexdigest():
+            return None
+        return int(kv["dram_bytes_per_launch_full_workload"])
+    except Exception:
+        return None
 
 
 def main():
@@ -174,12 +484,21 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-operator block")
     ap.add_argument("--batch", type=int, default=0,
                     help="sequences per GPU (default: the benchmark workload's 16); smaller values are for "
                          "profiler captures only and are reported in config.workload")
+    ap.add_argument("--op", choices=OPS, help="time one operator on one GPU and print one JSON line")
+    ap.add_argument("--save-stride", type=int, default=32)
+    ap.add_argument("--heads", type=int, default=32, help="Mamba-3: number of heads")
+    ap.add_argument("--headdim", type=int, default=64, help="Mamba-3: head dimension")
+    ap.add_argument("--dstate", type=int, default=128, help="Mamba-3: state size")
+    ap.add_argument("--sequential", action="store_true", help="Mamba-3 forward: the sequential kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.op:
+        return run_op(args)
 
     import torch
     import torch.distributed as dist
@@ -194,6 +513,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(args.warmup, 3)
@@ -225,6 +545,21 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- the product path is checked against the oracle before anything is timed ----
+    checked = None
+    if rank == 0:
+        import oracle
+        step()
+        torch.cuda.synchronize()
+        bs, ds = min(3, B - 1), [5, D - 7]
+        f = lambda t_: t_[bs:bs + 1].float().cpu().numpy()
+        ref = oracle.m1_fused_fwd(f(devt["x"])[..., ds], f(devt["delta_raw"])[..., ds], f(devt["Bm"]), f(devt["Cm"]),
+                                  f(devt["z"])[..., ds], inp["a_neg"][ds], inp["Dp"][ds])
+        err = float(np.abs(f(y)[..., ds] - ref["y"]).max() / np.abs(ref["y"]).max())
+        if not err <= 2e-2:
+            raise SystemExit(f"bench.py: the scan output differs from the oracle (rel err {err:.3g}): not timing it")
+        checked = {"against": "oracle.m1_fused_fwd, 1 sequence x 2 channels", "rel_err": err, "tol": 2e-2}
 
     # ---- device-resident throughput (value) + per-kernel time (roofline) ----
     for _ in range(warmup):
@@ -303,38 +638,29 @@ def main():
         f1.record()
         barrier()
         e2e_ms = f0.elapsed_time(f1) / n_e2e
+        del dev2, y2, yh2
     clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions
-
-    # ---- the training pair of the same workload (reported beside the headline, not part of it) ----
-    bwd = None
-    if rank == 0 and world == 1 and not args.no_e2e:
-        S = 32
-        cs = torch.empty(B, (T + S - 1) // S, D, N, device=dev)
-        dy = torch.randn(B, T, D, device=dev).to(td)
-        ws = torch.empty(mb.selective_scan_bwd_workspace_bytes(B, T, D, N), dtype=torch.uint8, device=dev)
-        mb.selective_scan_fwd(devt["x"], devt["delta_raw"], devt["Bm"], devt["Cm"], a_neg, Dp, devt["z"],
-                              chunk_states=cs, save_stride=S, y=y, handle=handle)
-        run_bwd = lambda: mb.selective_scan_bwd(devt["x"], devt["delta_raw"], devt["Bm"], devt["Cm"], a_neg, Dp,
-                                                dy, cs, S, devt["z"], workspace=ws, handle=handle)
-        for _ in range(3):
-            run_bwd()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(10):
-            run_bwd()
-        g1.record()
-        torch.cuda.synchronize()
-        bms = g0.elapsed_time(g1) / 10
-        bby = 7 * 2 * B * T * D + 2 * 2 * B * T * N + 2 * 4 * B * T * N + 4 * B * ((T + S - 1) // S) * D * N
-        bwd = {"ms": bms, "algorithmic_bytes": bby, "GBps": bby / (bms * 1e-3) / 1e9, "save_stride": S,
-               "kernels_per_call": 3}
-        del cs, dy, ws
 
     times = torch.tensor([total_ms, 0.0 if args.no_e2e else e2e_ms, kern_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, kern_ms = [float(v) for v in times.cpu()]
+
+    # ---- everything else on the path, after the headline region ----
+    extra = None
+    if not args.no_extra and not args.no_e2e:
+        del devt, y
+        torch.cuda.empty_cache()
+        if world == 1:
+            extra = {}
+            for name in ("sscan_fwd_random_a", "sscan_bwd", "conv1d_fwd", "conv1d_bwd", "sscan_fwd_small_batch",
+                         "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd"):
+                r = measure_op(name, dev)
+                r.pop("op")
+                extra[name] = r
+        else:
+            c = collective_extra(dev, world, rank)
+            extra = {"gradient_allreduce": c}
 
     if rank == 0:
         by = algorithmic_bytes(w)
@@ -343,50 +669,52 @@ def main():
         achieved = by / (kern_ms * 1e-3) / 1e9
         h2d = sum(v.numel() * v.element_size() for v in host.values())
         d2h = y_host.numel() * y_host.element_size()
+        cfgb = config_block(world)
+        cfgb["tokens_per_s"] = world * B * T / (ms_per_step * 1e-3)
         out = {
             "metric": METRIC, "value": world * by / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": workload_name(), "storage_dtype": "bf16", "global_batch": world * B,
-                       "seq_len": T, "tokens_per_s": world * B * T / (ms_per_step * 1e-3),
-                       "parallelism": f"batch-sharded x{world}, no collective on the scan",
-                       "l2": (f"inputs+outputs per step ({by / 1e6:.0f} MB) exceed the 126 MB L2" if by > 126e6 else
-                              f"inputs+outputs per step ({by / 1e6:.0f} MB) fit the 126 MB L2: not a valid bench size"),
-                       "a_neg": "S4D-real -(n+1): arithmetic-progression fast path (2 exp2 per step)"},
-            "clocks": clocks, "gpu_launches": args.steps,
+            "storage_dtype": "bf16", "data": "synthetic", "config": cfgb,
+            "clocks": clocks, "gpu_launches": args.steps, "checked_before_timing": checked,
             "e2e": (None if args.no_e2e else
                     {"value": world * by / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}),
+                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                     "staging_numa_node": numa,
+                     "note": "PCIe-bound: every rank uploads 304 MB and downloads 101 MB per step through the "
+                             "host's root complexes, which the GPUs of one box share"}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": ncu_traffic_bytes(), "peak_source": peak_src,
                          "kernel": "sscan_fwd_kernel", "kernel_ms": kern_ms,
                          "algorithmic_bytes": by},
         }
-        if bwd is not None:
-            bwd["frac_of_hbm_peak"] = bwd["GBps"] / peak
-            out["backward"] = bwd
+        if extra is not None:
+            if "sscan_fwd_random_a" in extra:
+                out["roofline"]["general_path_frac"] = extra["sscan_fwd_random_a"]["frac_of_hbm_peak"]
+                out["roofline"]["general_path_note"] = ("trained weights leave the arithmetic progression: one "
+                                                        "exp2 per state and step")
+            if "sscan_bwd" in extra:
+                out["backward"] = {"ms": extra["sscan_bwd"]["ms"],
+                                   "algorithmic_bytes": extra["sscan_bwd"]["algorithmic_bytes"],
+                                   "GBps": extra["sscan_bwd"]["GBps"], "save_stride": 32,
+                                   "frac_of_hbm_peak": extra["sscan_bwd"]["frac_of_hbm_peak"]}
+            out["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
-            val, cores, secs = cpu_leg(sample_B=B, sample_D=D)
+            cores = host_threads()
+            val, secs = cpu_scan_leg(sample_B=B, sample_D=D)
             out["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                                    "sample": f"the full workload ({B} sequences x {D} channels x L={T}), "
-                                             f"best of 5 passes after one warm-up, {secs:.2f} s per pass"}
+                                             f"best of 5 passes after one warm-up, {secs:.2f} s per pass",
+                                   "note": "the reference's Rust build is unavailable on this box (no cargo)"}
+            tps, psecs, pthreads = cpu_prefill_leg()
+            out["cpu_baseline"]["forward_prefill"] = {
+                "tokens_per_s": tps, "seconds_per_pass": psecs, "threads": pthreads,
+                "workload": "backbone prefill d_model 128, 2 layers, d_inner 256, d_state 16, batch 4 x 512 f32 "
+                            "(weights seed 42, inputs seed 7), one task per sample"}
         print(json.dumps(out))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-
-
-def ncu_traffic_bytes():
-    """dram read+write bytes of one launch of the dominant kernel from the ncu
-    capture summarised under profiles/ (None until one is committed)."""
-    p = os.path.join(ROOT, "profiles", "sscan_fwd_traffic.txt")
-    try:
-        for line in open(p):
-            if line.startswith("dram_bytes_per_launch_full_workload="):
-                return int(line.split("=", 1)[1])
-    except Exception:
-        pass
-    return None
 
 
 if __name__ == "__main__":

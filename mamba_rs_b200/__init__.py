@@ -10,4 +10,4 @@ from __future__ import annotations
 from . import ffi  # noqa: F401
 from .ffi import Handle, LibraryMissing, lib, lib_path  # noqa: F401
 from .ops import *  # noqa: F401,F403
-from .parallel import allreduce_grads, shard_batch  # noqa: F401,E402
+from .parallel import BucketedGradReducer, allreduce_grads, shard_batch  # noqa: F401,E402

@@ -556,7 +556,10 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             // instruction waits on the chain before it:
             //   elementwise of block k+2 | shuffles + decay seeds of block k+1 |
             //   recurrence and output of block k.
-            if (r_fast == 0 && nv == TC) {
+            // Full unrolling is kept to the kernels that carry the throughput (d_state <= 16,
+            // no fused conv, not the state-only pass): it multiplies their code size by 8.
+            constexpr bool kUnroll = LPC <= 2 && !kConv && !kStateOnly;
+            if (kUnroll && r_fast == 0 && nv == TC) {
                 // a whole chunk: fully unrolled, the stage hand-over is register renaming
                 constexpr int NB = TC / RB;
                 Elem el[NB + 2][OWN];

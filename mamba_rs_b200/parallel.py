@@ -15,7 +15,7 @@ from typing import Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_batch", "allreduce_grads", "init_from_env"]
+__all__ = ["shard_batch", "allreduce_grads", "init_from_env", "BucketedGradReducer"]
 
 
 def shard_batch(global_batch: int, rank: int, world: int) -> Tuple[int, int]:
@@ -70,3 +70,62 @@ def allreduce_grads(flat_grads: torch.Tensor, group=None, bucket_bytes: int = 64
     if average:
         flat_grads.div_(dist.get_world_size(group))
     return flat_grads
+
+
+class BucketedGradReducer:
+    """All-reduce of the flat f32 gradient arena, one bucket per layer, overlapped
+    with the rest of the backward.
+
+    The backward walks the layers last to first; as soon as a layer's parameter
+    gradients are complete the caller names its bucket with ``bucket_ready(i)``:
+    the sum over ranks of that slice is issued on a side stream (NCCL over
+    NVLink on GPUs), ordered after the work already queued on the caller's stream,
+    and runs under the backward kernels of the layers still to come.
+    ``finish()`` joins the side stream (and divides by the world size when
+    averaging).  With a CPU tensor (gloo) the same calls run without streams.
+    The reference keeps this arena as ``GpuMambaGrads.flat``
+    (src/mamba_ssm/gpu/weights.rs:487-560) and has no collective of its own; the
+    place it would sit is between backward and optimiser,
+    src/mamba_ssm/gpu/trainer.rs:1476-1481."""
+
+    def __init__(self, flat_grads: torch.Tensor, bounds, group=None, average: bool = False):
+        if flat_grads.dtype != torch.float32 or not flat_grads.is_contiguous() or flat_grads.dim() != 1:
+            raise TypeError("the gradient arena is one contiguous 1-D float32 tensor")
+        self.flat, self.group, self.average = flat_grads, group, average
+        self.bounds = [(int(lo), int(hi)) for lo, hi in bounds]
+        for lo, hi in self.bounds:
+            if not (0 <= lo <= hi <= flat_grads.numel()):
+                raise ValueError(f"bucket [{lo}, {hi}) outside the arena of {flat_grads.numel()} elements")
+        self.active = dist.is_initialized() and dist.get_world_size(group) > 1
+        self.cuda = flat_grads.is_cuda
+        self.side = torch.cuda.Stream(device=flat_grads.device) if (self.cuda and self.active) else None
+        self.works = []
+        self.done = set()
+
+    def bucket_ready(self, i: int):
+        if i in self.done:
+            raise ValueError(f"bucket {i} was already reduced")
+        self.done.add(i)
+        if not self.active:
+            return
+        lo, hi = self.bounds[i]
+        view = self.flat[lo:hi]
+        if self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream(self.flat.device))
+            with torch.cuda.stream(self.side):
+                self.works.append(dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        else:
+            self.works.append(dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self) -> torch.Tensor:
+        for w in self.works:
+            w.wait()
+        self.works = []
+        if self.side is not None:
+            torch.cuda.current_stream(self.flat.device).wait_stream(self.side)
+        if self.active and self.average:
+            n = dist.get_world_size(self.group)
+            for i in self.done:
+                lo, hi = self.bounds[i]
+                self.flat[lo:hi].div_(n)
+        return self.flat

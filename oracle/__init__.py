@@ -264,6 +264,18 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int | None = None) -> int:
+    """Use `n` OpenMP threads from now on (default: every core this process may run
+    on), whatever OMP_NUM_THREADS said when the library was loaded.  Returns n."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().orc_set_num_threads(C.c_int(int(n)))
+    return int(n)
+
+
 # -- seeded test inputs ------------------------------------------------------
 
 def det_rand(n: int, seed: int) -> np.ndarray:

@@ -661,6 +661,16 @@ ORC_API int orc_m1_prefill_batch(const OrcM1Config *c, const float *w, const flo
     return nthreads;
 }
 
+/* Sets the OpenMP team size for later calls (a launcher such as torchrun exports
+ * OMP_NUM_THREADS=1 to its workers; the CPU baseline wants every host core). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 
 import oracle
 from helpers import quantised_inputs, rel_err
-from mamba_rs_b200.parallel import allreduce_grads, shard_batch
+from mamba_rs_b200.parallel import BucketedGradReducer, allreduce_grads, shard_batch
 
 
 def test_shard_batch_partitions_every_sequence_once():
@@ -57,6 +57,14 @@ def _worker(rank, world, port, B, T, D, N, out_dir):
         arena = torch.from_numpy(flat.copy())
         allreduce_grads(arena, bucket_bytes=256)  # several buckets
         np.save(os.path.join(out_dir, f"arena{rank}.npy"), arena.numpy())
+        # the per-layer reducer: buckets named last to first, as a backward pass finishes them
+        arena2 = torch.from_numpy(flat.copy())
+        cut = D * N
+        red = BucketedGradReducer(arena2, [(0, cut), (cut, cut + D)])
+        red.bucket_ready(1)
+        red.bucket_ready(0)
+        red.finish()
+        np.save(os.path.join(out_dir, f"arena_b{rank}.npy"), arena2.numpy())
         np.save(os.path.join(out_dir, f"dB{rank}.npy"), per_seq)
     finally:
         dist.destroy_process_group()
@@ -75,6 +83,8 @@ def test_sharded_gradients_allreduce_to_the_whole_batch(tmp_path, world, B):
     for a in arenas[1:]:
         np.testing.assert_array_equal(a, arenas[0])  # every rank holds the same sum
     assert rel_err(arenas[0], ref) <= 1e-5  # only the summation order over samples differs
+    for r in range(world):  # the bucketed reducer gives the same sums as the flat all-reduce
+        np.testing.assert_array_equal(np.load(tmp_path / f"arena_b{r}.npy"), arenas[0])
     # per-sequence outputs need no exchange: the shards concatenate to the whole
     dB = np.concatenate([np.load(tmp_path / f"dB{r}.npy") for r in range(world)], axis=0)
     np.testing.assert_array_equal(dB, whole["dB"])
