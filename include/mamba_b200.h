@@ -129,6 +129,44 @@ MAMBA_B200_API int mamba_b200_ssm_scan_fwd_nosave(void* handle, void* stream, in
                                    int T, int d_inner, int d_state);
 
 /*
+ * The saving forward and the backward with the reference kernels' own buffers, for a
+ * call-site swap without re-plumbing the trainer's activations:
+ *   mamba_b200_ssm_scan_fwd_save : argument list of ssm_parallel_scan_fwd_{dt} /
+ *       ssm_burnin_forward_{dt} (kernels/mamba_ssm_parallel.cu:265-276, :777-790,
+ *       kernels/mamba_ssm.cu:232-246; launch src/mamba_ssm/gpu/forward_mixed.rs:632-702).
+ *       h_saved is the reference's [batch, T+1, d_inner, d_state] f32 buffer; only its
+ *       rows 0, 32, 64, ... (the states entering each 32-step block) are written, which is
+ *       all mamba_b200_ssm_scan_bwd reads.  The reference's own backward kernels need
+ *       every row: pair this forward with this backward, not with theirs.
+ *   mamba_b200_ssm_scan_bwd : replaces ssm_parallel_scan_bwd_{dt} / ssm_backward_local_{dt}
+ *       AND the four reducers ssm_reduce_d_{B,C,D,a_log} in one call
+ *       (kernels/mamba_ssm_parallel.cu:1182-1200, kernels/mamba_ssm.cu:466-763; launch
+ *       src/mamba_ssm/gpu/backward_mixed.rs:205-348).  Same inputs in the same order; the
+ *       [B,T,D,N] d_B_local / d_C_local and the per-sample d_D_local / d_a_log_local
+ *       partials do not exist here, so the outputs are the reducers' outputs:
+ *       d_B, d_C [batch, T, d_state] f32 (overwritten), d_D [d_inner], d_a_log
+ *       [d_inner, d_state] f32 (+=), plus a caller workspace of
+ *       mamba_b200_sscan_bwd_workspace_bytes(batch, T, d_inner, d_state) bytes.
+ *   mamba_b200_conv1d_fwd_nosave : argument list of conv1d_burnin_forward_nosave_{dt}
+ *       (kernels/conv1d.cu:284-296; launch src/mamba_ssm/gpu/prefill.rs:788).
+ * The saving conv forward and the conv backward have no such twin: the reference's pair
+ * exchanges post_conv [B,T,D] and conv_states [B,T,D,K] (kernels/conv1d.cu:326-338,
+ * :459-470), which this library never materialises; mamba_b200_conv1d_bwd takes x itself.
+ */
+MAMBA_B200_API int mamba_b200_ssm_scan_fwd_save(void* handle, void* stream, int dtype, float* h, void* y_out,
+                                 float* h_saved, const void* delta, const void* u, const void* B,
+                                 const void* C, const float* a_neg, const float* D, int batch, int T,
+                                 int d_inner, int d_state);
+MAMBA_B200_API int mamba_b200_ssm_scan_bwd(void* handle, void* stream, int dtype, const float* h_saved,
+                            const void* delta, const void* u, const void* B, const void* C,
+                            const float* a_neg, const float* D, const void* dy, void* d_delta, void* d_u,
+                            float* d_B, float* d_C, float* d_D, float* d_a_log, int batch, int T, int d_inner,
+                            int d_state, void* workspace, long long workspace_bytes);
+MAMBA_B200_API int mamba_b200_conv1d_fwd_nosave(void* handle, void* stream, int dtype, void* u_out, float* state,
+                                 const void* x_branch, const float* weight, const float* bias, int batch,
+                                 int T, int d_inner, int d_conv);
+
+/*
  * Mamba-1 fused backward (BPTT) by recomputation.  One call replaces, per layer,
  * gating_backward_{dt} (kernels/elementwise.cu:191-233), the B/C gather,
  * ssm_parallel_scan_bwd_{dt} / ssm_backward_local_{dt}
@@ -147,7 +185,7 @@ MAMBA_B200_API int mamba_b200_ssm_scan_fwd_nosave(void* handle, void* stream, in
  */
 typedef struct mamba_b200_sscan_bwd_args {
     int dtype;
-    int B, T, D, N;        /* N <= 16 */
+    int B, T, D, N;        /* N <= 256; N <= 16 (every shipped Mamba-1 model) takes the tuned kernels */
     const void* u;         /* [B*T, ld_u] scan input (post conv + SiLU) */
     long long ld_u;
     const void* delta;     /* as given to the forward */

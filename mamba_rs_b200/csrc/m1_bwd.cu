@@ -199,11 +199,10 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
         // ---- 2. state entering each sub-block ----
         float h[NS];
         {
-            const long long nsave = nblk;
 #pragma unroll
             for (int j = 0; j < NS; ++j)
                 h[j] = (d_ok && j < N)
-                           ? p.chunk_states[((static_cast<long long>(b) * nsave + k) * D + d) * N + j]
+                           ? p.chunk_states[b * p.cs_ld_b + k * p.cs_ld_k + static_cast<long long>(d) * N + j]
                            : 0.0f;
         }
         const int nsub = (nv + kBwdSub - 1) / kBwdSub;
@@ -402,7 +401,7 @@ __global__ void __launch_bounds__(32) sscan_densify_kernel(const BwdParams p, fl
     if (d >= D) return;
     const int nb64 = (T + 63) / 64, nb32 = (T + 31) / 32;
     float h[8], a2[8];
-    const float* cs = p.chunk_states + ((static_cast<long long>(b) * nb64 + k) * D + d) * N;
+    const float* cs = p.chunk_states + b * p.cs_ld_b + k * p.cs_ld_k + static_cast<long long>(d) * N;
     float* o0 = dense + ((static_cast<long long>(b) * nb32 + 2 * k) * D + d) * N;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -513,6 +512,7 @@ static const Bwd2Table& bwd2_table() {
 }
 
 int m1_bwd_configure(Ctx* c) {
+    MB200_CUDA_CHECK(c, bwd_wide_configure());
     const Bwd2Table& t2 = bwd2_table();
     for (int dt = 0; dt < 3; ++dt)
         for (int si = 0; si < 2; ++si)
@@ -537,11 +537,22 @@ int m1_bwd_configure(Ctx* c) {
 
 static int bwd_ns(int N) { return N <= 4 ? 4 : (N <= 8 ? 8 : 16); }
 
+// m1_bwd_wide.cu: 16 < d_state <= 256
+int bwd_wide_lpc(int N);
+size_t bwd_wide_smem(int N, int S);
+cudaError_t bwd_wide_configure();
+cudaError_t launch_bwd_wide(const BwdParams& p, int dtype, int softplus, cudaStream_t st, int* tiles);
+
 static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off_d, size_t* off_dense,
                           size_t* total) {
     // channel tiles of the dB/dC partials: 16 channels per CTA for the two-lane
     // kernel (d_state > 8), 32 for the one-lane kernel
-    const size_t tiles = N > 8 ? (D + 15) / 16 : (D + 31) / 32, V = 2 * bwd_ns(N);
+    size_t tiles = N > 8 ? (D + 15) / 16 : (D + 31) / 32, V = 2 * bwd_ns(N);
+    if (N > 16) {  // wide-state kernel: 32 / LPC channels per warp, rows of 2 * (8 * LPC) partials
+        const int lpc = bwd_wide_lpc(N);
+        tiles = (D + 32 / lpc - 1) / (32 / lpc);
+        V = 2 * 8 * lpc;
+    }
     size_t bc = sizeof(float) * static_cast<size_t>(B) * tiles * T * V;
     bc = (bc + 255) & ~size_t(255);
     size_t a = sizeof(float) * static_cast<size_t>(B) * D * N;
@@ -551,7 +562,7 @@ static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off
     *off_d = bc + a;
     *off_dense = bc + a + ((dd + 255) & ~size_t(255));
     // states every 32 steps, rebuilt from a stride-64 save (two-lane kernel only)
-    const size_t dense = N > 8 ? sizeof(float) * static_cast<size_t>(B) * ((T + 31) / 32) * D * N : 0;
+    const size_t dense = (N > 8 && N <= 16) ? sizeof(float) * static_cast<size_t>(B) * ((T + 31) / 32) * D * N : 0;
     *total = *off_dense + ((dense + 255) & ~size_t(255));
 }
 
@@ -560,22 +571,18 @@ static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off
 using namespace mb200;
 
 extern "C" MAMBA_B200_API long long mamba_b200_sscan_bwd_workspace_bytes(int B, int T, int D, int N) {
-    if (B <= 0 || T <= 0 || D <= 0 || N <= 0 || N > 16) return 0;
+    if (B <= 0 || T <= 0 || D <= 0 || N <= 0 || N > 256) return 0;
     size_t a, d, dn, total;
     bwd_ws_layout(B, T, D, N, &a, &d, &dn, &total);
     return static_cast<long long>(total);
 }
 
-extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
-                                                   const mamba_b200_sscan_bwd_args* ap) {
-    Ctx* c = static_cast<Ctx*>(handle);
-    if (!c) return MAMBA_B200_ERR_ARG;
-    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: null args");
-    const mamba_b200_sscan_bwd_args& a = *ap;
+static int launch_bwd(Ctx* c, void* stream, const mamba_b200_sscan_bwd_args& a, long long cs_ld_b,
+                      long long cs_ld_k) {
     if (!dtype_ok(a.dtype)) return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: bad dtype %d", a.dtype);
     if (a.B < 0 || a.T < 0 || a.D <= 0 || a.N <= 0)
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: bad dims B=%d T=%d D=%d N=%d", a.B, a.T, a.D, a.N);
-    if (a.N > 16) return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_bwd: d_state %d > 16 is not supported", a.N);
+    if (a.N > 256) return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_bwd: d_state %d > 256", a.N);
     if (a.B == 0 || a.T == 0) return MAMBA_B200_OK;
     if (a.B > 65535) return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_bwd: batch %d > 65535", a.B);
     if (!a.u || !a.delta || !a.Bm || !a.Cm || !a.a_neg || !a.Dp || !a.dy || !a.chunk_states || !a.d_u ||
@@ -603,12 +610,33 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
     p.ld_u = a.ld_u; p.ld_dl = a.ld_delta; p.ld_z = a.ld_z; p.ld_dy = a.ld_dy; p.ld_bc = a.ld_bc;
     p.ld_du = a.ld_du; p.ld_ddl = a.ld_ddelta; p.ld_dz = a.ld_dz;
     p.a_neg = a.a_neg; p.Dp = a.Dp; p.chunk_states = a.chunk_states;
+    p.cs_ld_k = cs_ld_k ? cs_ld_k : static_cast<long long>(a.D) * a.N;
+    p.cs_ld_b = cs_ld_b ? cs_ld_b : p.cs_ld_k * ((a.T + a.save_stride - 1) / a.save_stride);
     unsigned char* ws = static_cast<unsigned char*>(a.workspace);
     p.part_bc = reinterpret_cast<float*>(ws);
     p.part_a = reinterpret_cast<float*>(ws + off_a);
     p.part_d = reinterpret_cast<float*>(ws + off_d);
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.S = a.save_stride; p.z_mode = a.z_mode;
     p.status = c->d_status;
+    cudaStream_t stw = static_cast<cudaStream_t>(stream);
+    if (a.N > 16) {
+        if (bwd_wide_smem(a.N, a.save_stride) > 227 * 1024)
+            return fail(c, MAMBA_B200_ERR_SHAPE, "sscan_bwd: d_state %d with save_stride %d needs more shared memory "
+                        "than an SM has; save every 32 steps", a.N, a.save_stride);
+        int wtiles = 0;
+        cudaError_t e = launch_bwd_wide(p, a.dtype, a.delta_softplus, stw, &wtiles);
+        if (e != cudaSuccess) return fail(c, MAMBA_B200_ERR_CUDA, "sscan_bwd (wide): %s", cudaGetErrorString(e));
+        const int np = 8 * bwd_wide_lpc(a.N);
+        const long long nbcw = static_cast<long long>(a.B) * a.T * 2 * np;
+        bwd_reduce_bc_kernel<<<static_cast<unsigned>((nbcw + 255) / 256), 256, 0, stw>>>(
+            p.part_bc, a.dBm, a.dCm, a.B, a.T, a.N, np, wtiles);
+        MB200_CUDA_CHECK(c, cudaGetLastError());
+        const int npar = a.D * a.N;
+        bwd_reduce_params_kernel<<<(npar + 255) / 256, 256, 0, stw>>>(p.part_a, p.part_d, a.dA_log, a.dD, a.B, a.D,
+                                                                    a.N);
+        MB200_CUDA_CHECK(c, cudaGetLastError());
+        return MAMBA_B200_OK;
+    }
     // one lane per channel for d_state <= 8, two lanes above
     const bool two_lane = a.N > 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -623,6 +651,8 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
         MB200_CUDA_CHECK(c, cudaGetLastError());
         p.chunk_states = dense;
         p.S = S = 32;
+        p.cs_ld_k = static_cast<long long>(a.D) * a.N;
+        p.cs_ld_b = p.cs_ld_k * ((a.T + 31) / 32);
     }
     const int DT = two_lane ? 16 : 32;  // channels per CTA
     unsigned m = 0;
@@ -660,4 +690,36 @@ extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
                                                              a.D, a.N);
     MB200_CUDA_CHECK(c, cudaGetLastError());
     return MAMBA_B200_OK;
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_sscan_bwd(void* handle, void* stream,
+                                                   const mamba_b200_sscan_bwd_args* ap) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!ap) return fail(c, MAMBA_B200_ERR_ARG, "sscan_bwd: null args");
+    return launch_bwd(c, stream, *ap, 0, 0);
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_ssm_scan_bwd(void* handle, void* stream, int dtype, const float* h_saved,
+                                                      const void* delta, const void* u, const void* B,
+                                                      const void* C, const float* a_neg, const float* D,
+                                                      const void* dy, void* d_delta, void* d_u, float* d_B,
+                                                      float* d_C, float* d_D, float* d_a_log, int batch, int T,
+                                                      int d_inner, int d_state, void* workspace,
+                                                      long long workspace_bytes) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    mamba_b200_sscan_bwd_args a;
+    memset(&a, 0, sizeof(a));
+    a.dtype = dtype; a.B = batch; a.T = T; a.D = d_inner; a.N = d_state;
+    a.u = u; a.ld_u = d_inner; a.delta = delta; a.ld_delta = d_inner; a.delta_softplus = 0;
+    a.Bm = B; a.Cm = C; a.ld_bc = d_state; a.z_mode = 0;
+    a.a_neg = a_neg; a.Dp = D;
+    a.chunk_states = h_saved; a.save_stride = 32;  // rows 0, 32, 64, ... of h_saved [batch, T+1, d_inner, d_state]
+    a.dy = dy; a.ld_dy = d_inner;
+    a.d_u = d_u; a.ld_du = d_inner; a.d_delta = d_delta; a.ld_ddelta = d_inner;
+    a.dBm = d_B; a.dCm = d_C; a.dA_log = d_a_log; a.dD = d_D;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+    const long long row = static_cast<long long>(d_inner) * d_state;
+    return launch_bwd(c, stream, a, row * (static_cast<long long>(T) + 1), 32 * row);
 }

@@ -44,6 +44,10 @@ struct BwdParams {
     void *du, *ddl, *dz;
     long long ld_u, ld_dl, ld_z, ld_dy, ld_bc, ld_du, ld_ddl, ld_dz;
     const float *a_neg, *Dp, *chunk_states;
+    // saved state k of sample b starts at chunk_states + b * cs_ld_b + k * cs_ld_k
+    // ([B, blocks, D, N] from the fused forward; rows 0, S, 2S... of the reference's
+    // h_saved [B, T+1, D, N] through the compat entry point)
+    long long cs_ld_b, cs_ld_k;
     float *part_bc;  // [B][tiles][T][2N]
     float *part_a;   // [B][D][N]
     float *part_d;   // [B][D]
@@ -263,7 +267,8 @@ __global__ void __maxnreg__(kBwd2MaxRegs) sscan_bwd2_kernel(const __grid_constan
             };
 
             // ---- 2. state entering each sub-block ----
-            const float* cs = p.chunk_states + ((static_cast<long long>(b) * nblk + k) * D + (d_ok ? d : 0)) * N + n0;
+            const float* cs = p.chunk_states + b * p.cs_ld_b + k * p.cs_ld_k +
+                              static_cast<long long>(d_ok ? d : 0) * N + n0;
             auto load_entry = [&](int sb, float2* h) {
                 if (sb == 0) {
                     float hv[8];

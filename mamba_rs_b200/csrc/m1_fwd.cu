@@ -78,7 +78,8 @@ static bool overlaps(const void* a, size_t na, const void* b, size_t nb) {
     return a && b && x < y + nb && y < x + na;
 }
 
-static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_args& a) {
+static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_args& a, long long cs_ld_b = 0,
+                      long long cs_ld_k = 0) {
     if (!dtype_ok(a.dtype)) return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: bad dtype %d", a.dtype);
     if (a.B < 0 || a.T < 0 || a.D <= 0 || a.N <= 0)
         return fail(c, MAMBA_B200_ERR_ARG, "sscan_fwd: bad dims B=%d T=%d D=%d N=%d", a.B, a.T, a.D, a.N);
@@ -129,6 +130,10 @@ static int launch_fwd(Ctx* c, cudaStream_t stream, const mamba_b200_sscan_fwd_ar
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.K = a.conv_w ? a.K : 0;
     p.z_mode = a.z_mode;
     p.save_stride = a.chunk_states ? a.save_stride : 1;
+    if (a.chunk_states) {  // default: dense [B, ceil(T / stride), D, N]
+        p.cs_ld_k = cs_ld_k ? cs_ld_k : static_cast<long long>(a.D) * a.N;
+        p.cs_ld_b = cs_ld_b ? cs_ld_b : p.cs_ld_k * ((a.T + a.save_stride - 1) / a.save_stride);
+    }
     p.status = c->d_status;
     unsigned m = 0;
     const int xrows = a.conv_w ? v->tc + kHaloRows : v->tc;
@@ -228,4 +233,24 @@ extern "C" MAMBA_B200_API int mamba_b200_ssm_scan_fwd_nosave(void* handle, void*
     a.Bm = B; a.Cm = C; a.ld_bc = d_state; a.z_mode = 0;
     a.a_neg = a_neg; a.Dp = D; a.ssm_state = h; a.y = y_out; a.ld_y = d_inner;
     return launch_fwd(c, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" MAMBA_B200_API int mamba_b200_ssm_scan_fwd_save(void* handle, void* stream, int dtype, float* h,
+                                                           void* y_out, float* h_saved, const void* delta,
+                                                           const void* u, const void* B, const void* C,
+                                                           const float* a_neg, const float* D, int batch, int T,
+                                                           int d_inner, int d_state) {
+    Ctx* c = static_cast<Ctx*>(handle);
+    if (!c) return MAMBA_B200_ERR_ARG;
+    if (!h_saved) return fail(c, MAMBA_B200_ERR_ARG, "ssm_scan_fwd_save: null h_saved");
+    mamba_b200_sscan_fwd_args a;
+    memset(&a, 0, sizeof(a));
+    a.dtype = dtype; a.B = batch; a.T = T; a.D = d_inner; a.N = d_state;
+    a.x = u; a.ld_x = d_inner; a.delta = delta; a.ld_delta = d_inner; a.delta_softplus = 0;
+    a.Bm = B; a.Cm = C; a.ld_bc = d_state; a.z_mode = 0;
+    a.a_neg = a_neg; a.Dp = D; a.ssm_state = h; a.y = y_out; a.ld_y = d_inner;
+    // rows 0, 32, 64, ... of h_saved [batch, T+1, d_inner, d_state]
+    a.chunk_states = h_saved; a.save_stride = 32;
+    const long long row = static_cast<long long>(d_inner) * d_state;
+    return launch_fwd(c, static_cast<cudaStream_t>(stream), a, row * (static_cast<long long>(T) + 1), 32 * row);
 }

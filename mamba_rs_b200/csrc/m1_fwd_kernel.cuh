@@ -39,6 +39,7 @@ struct FwdParams {
     long long ld_x, ld_dl, ld_z, ld_bc, ld_y, ld_u;
     const float *a_neg, *Dp, *conv_w, *conv_b;
     float *conv_state, *ssm_state, *chunk_states;   // conv / ssm state: written at the end
+    long long cs_ld_b, cs_ld_k;   // saved state k of sample b starts at chunk_states + b*cs_ld_b + k*cs_ld_k
     const float *conv_in, *ssm_in;                  // entering conv window / state (read)
     float *conv_copy, *ssm_copy;  // state-only pass, segment 0: keeps the entering state for the second pass
     // Time segments (grid.z > 1): segment s > 0 starts from seg_states[b][s-1] and
@@ -303,7 +304,6 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
             p.conv_copy[(static_cast<long long>(b) * D + d) * K + k] =
                 p.conv_in ? p.conv_in[(static_cast<long long>(b) * D + d) * K + k] : 0.0f;
     const bool gate_is_silu = p.z_mode == 1;
-    const long long save_chunks = p.chunk_states ? (T + p.save_stride - 1) / p.save_stride : 0;
     float sum_dl = 0.0f;  // state-only pass: sum of this segment's deltas (owner rows only)
 
     Tact* yg = static_cast<Tact*>(p.y);
@@ -340,7 +340,7 @@ sscan_fwd_kernel(const __grid_constant__ FwdParams p) {
         // Training save: state entering each block of save_stride steps.
         if (!kStateOnly && p.chunk_states && (t0 % p.save_stride) == 0) {
             const long long sc = t0 / p.save_stride;
-            float* dst = p.chunk_states + ((static_cast<long long>(b) * save_chunks + sc) * D + d) * N;
+            float* dst = p.chunk_states + b * p.cs_ld_b + sc * p.cs_ld_k + static_cast<long long>(d) * N;
 #pragma unroll
             for (int j = 0; j < NS; ++j)
                 if (d_ok && n0 + j < N) dst[n0 + j] = (j & 1) ? h[j / 2].y : h[j / 2].x;

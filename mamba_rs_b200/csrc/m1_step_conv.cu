@@ -724,3 +724,15 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd_static(void* handle, void* s
     Ctx local;
     return mamba_b200_conv1d_bwd(c ? c : &local, stream, &a);
 }
+
+extern "C" MAMBA_B200_API int mamba_b200_conv1d_fwd_nosave(void* handle, void* stream, int dtype, void* u_out,
+                                                           float* state, const void* x_branch, const float* weight,
+                                                           const float* bias, int batch, int T, int d_inner,
+                                                           int d_conv) {
+    mamba_b200_conv1d_args a;
+    memset(&a, 0, sizeof(a));
+    a.dtype = dtype; a.B = batch; a.T = T; a.D = d_inner; a.K = d_conv;
+    a.x = x_branch; a.ld_x = d_inner; a.conv_w = weight; a.conv_b = bias; a.conv_state = state;
+    a.u = u_out; a.ld_u = d_inner;
+    return mamba_b200_conv1d_fwd(handle, stream, &a);
+}

@@ -137,6 +137,10 @@ def lib() -> C.CDLL:
         bind("mamba_b200_sscan_fwd", [vp, vp, C.POINTER(SscanFwdArgs)])
         bind("mamba_b200_sscan_fwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
         bind("mamba_b200_sscan_bwd", [vp, vp, C.POINTER(SscanBwdArgs)])
+        bind("mamba_b200_ssm_scan_fwd_nosave", [vp, vp, C.c_int] + [vp] * 8 + [C.c_int] * 4)
+        bind("mamba_b200_ssm_scan_fwd_save", [vp, vp, C.c_int] + [vp] * 9 + [C.c_int] * 4)
+        bind("mamba_b200_ssm_scan_bwd", [vp, vp, C.c_int] + [vp] * 14 + [C.c_int] * 4 + [vp, C.c_longlong])
+        bind("mamba_b200_conv1d_fwd_nosave", [vp, vp, C.c_int] + [vp] * 5 + [C.c_int] * 4)
         bind("mamba_b200_sscan_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
         bind("mamba_b200_sscan_step", [vp, vp, C.POINTER(SscanStepArgs)])
         bind("mamba_b200_conv1d_fwd", [vp, vp, C.POINTER(Conv1dArgs)])

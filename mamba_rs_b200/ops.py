@@ -17,7 +17,7 @@ from . import ffi
 
 __all__ = ["selective_scan_fwd", "selective_scan_fwd_workspace_bytes", "selective_scan_bwd",
            "selective_scan_bwd_workspace_bytes",
-           "ssm_parallel_scan_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
+           "ssm_parallel_scan_fwd_nosave", "ssm_scan_fwd_save", "ssm_scan_bwd", "conv1d_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -122,6 +122,76 @@ def ssm_parallel_scan_fwd_nosave(h_state, y_out, delta, u, Bm, Cm, a_neg, Dp, *,
                 C.c_int(T), C.c_int(D), C.c_int(N))
     hd.check(rc, "mamba_b200_ssm_scan_fwd_nosave")
     return y_out
+
+
+def ssm_scan_fwd_save(h_state, y_out, h_saved, delta, u, Bm, Cm, a_neg, Dp, *, handle=None):
+    """Drop-in for the reference's saving forward ``ssm_parallel_scan_fwd_{dt}``
+    (kernels/mamba_ssm_parallel.cu:777-790): same tensors; of ``h_saved``
+    [B, T+1, D, N] only rows 0, 32, 64, ... are written (what ssm_scan_bwd reads)."""
+    _require_cuda(h_state, y_out, h_saved, delta, u, Bm, Cm, a_neg, Dp)
+    Bsz, T, D = delta.shape
+    N = a_neg.shape[1]
+    dev = delta.device
+    hd = handle or ffi.default_handle(dev.index or 0)
+    if tuple(h_saved.shape) != (Bsz, T + 1, D, N) or h_saved.dtype != torch.float32 or not h_saved.is_contiguous():
+        raise ValueError("h_saved must be contiguous float32 [B, T+1, D, N]")
+    for t in (y_out, delta, u, Bm, Cm, a_neg, Dp, h_state):
+        if not t.is_contiguous():
+            raise ValueError("compat entry point takes contiguous tensors")
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_ssm_scan_fwd_save(
+            hd.ptr, _stream(dev), C.c_int(dtype_code(delta.dtype)), _ptr(h_state), _ptr(y_out), _ptr(h_saved),
+            _ptr(delta), _ptr(u), _ptr(Bm), _ptr(Cm), _ptr(a_neg), _ptr(Dp), Bsz, T, D, N)
+    hd.check(rc, "mamba_b200_ssm_scan_fwd_save")
+    return y_out
+
+
+def ssm_scan_bwd(h_saved, delta, u, Bm, Cm, a_neg, Dp, dy, *, d_D=None, d_a_log=None, workspace=None,
+                 handle=None):
+    """Drop-in for ``ssm_parallel_scan_bwd_{dt}`` / ``ssm_backward_local_{dt}`` plus the four
+    reducers (kernels/mamba_ssm_parallel.cu:1182-1200, kernels/mamba_ssm.cu:466-763), on the
+    reference's own buffers.  Returns dict(d_delta, d_u, dB, dC, dD, dA_log); d_D / d_a_log
+    are accumulated into the tensors passed in (zeros otherwise)."""
+    _require_cuda(h_saved, delta, u, Bm, Cm, a_neg, Dp, dy, d_D, d_a_log, workspace)
+    Bsz, T, D = delta.shape
+    N = a_neg.shape[1]
+    dev = delta.device
+    hd = handle or ffi.default_handle(dev.index or 0)
+    for t in (h_saved, delta, u, Bm, Cm, a_neg, Dp, dy):
+        if not t.is_contiguous():
+            raise ValueError("compat entry point takes contiguous tensors")
+    f32 = dict(dtype=torch.float32, device=dev)
+    d_delta, d_u = torch.empty_like(delta), torch.empty_like(u)
+    dB, dC = torch.empty((Bsz, T, N), **f32), torch.empty((Bsz, T, N), **f32)
+    d_D = torch.zeros(D, **f32) if d_D is None else d_D
+    d_a_log = torch.zeros((D, N), **f32) if d_a_log is None else d_a_log
+    if workspace is None:
+        workspace = torch.empty(max(selective_scan_bwd_workspace_bytes(Bsz, T, D, N), 1), dtype=torch.uint8,
+                                device=dev)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_ssm_scan_bwd(
+            hd.ptr, _stream(dev), C.c_int(dtype_code(delta.dtype)), _ptr(h_saved), _ptr(delta), _ptr(u), _ptr(Bm),
+            _ptr(Cm), _ptr(a_neg), _ptr(Dp), _ptr(dy), _ptr(d_delta), _ptr(d_u), _ptr(dB), _ptr(dC), _ptr(d_D),
+            _ptr(d_a_log), Bsz, T, D, N, _ptr(workspace), C.c_longlong(workspace.numel()))
+    hd.check(rc, "mamba_b200_ssm_scan_bwd")
+    return dict(d_delta=d_delta, d_u=d_u, dB=dB, dC=dC, dD=d_D, dA_log=d_a_log)
+
+
+def conv1d_fwd_nosave(u_out, state, x, conv_w, conv_b, *, handle=None):
+    """Drop-in for ``conv1d_burnin_forward_nosave_{dt}`` (kernels/conv1d.cu:284-296)."""
+    _require_cuda(u_out, state, x, conv_w, conv_b)
+    Bsz, T, D = x.shape
+    dev = x.device
+    hd = handle or ffi.default_handle(dev.index or 0)
+    for t in (u_out, state, x, conv_w, conv_b):
+        if not t.is_contiguous():
+            raise ValueError("compat entry point takes contiguous tensors")
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_conv1d_fwd_nosave(hd.ptr, _stream(dev), C.c_int(dtype_code(x.dtype)), _ptr(u_out),
+                                                    _ptr(state), _ptr(x), _ptr(conv_w), _ptr(conv_b), Bsz, T, D,
+                                                    conv_w.shape[1])
+    hd.check(rc, "mamba_b200_conv1d_fwd_nosave")
+    return u_out
 
 
 def selective_scan_fwd_workspace_bytes(B, T, D, N) -> int:

@@ -36,7 +36,9 @@ def gpu_fwd_bwd(q, dg, dt, dev, ssm0, S, delta_softplus=True):
 
 
 SHAPES = [(2, 40, 64, 16), (1, 1, 32, 16), (1, 15, 33, 16), (1, 17, 7, 16), (2, 64, 32, 16),
-          (1, 65, 40, 16), (3, 100, 20, 8), (1, 130, 12, 4), (1, 50, 12, 12), (2, 200, 96, 16)]
+          (1, 65, 40, 16), (3, 100, 20, 8), (1, 130, 12, 4), (1, 50, 12, 12), (2, 200, 96, 16),
+          # d_state > 16: the wide-state kernel (4 ... 32 lanes per channel)
+          (2, 70, 20, 32), (1, 100, 9, 64), (1, 40, 5, 24), (1, 33, 3, 128), (1, 65, 2, 256)]
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])

@@ -87,6 +87,64 @@ def test_reference_scan_backward_agrees_with_oracle_and_library(cuda_dev, rk, sh
         assert rel_err(host(lib[gk]), host(ref[gk])) <= tol, ("library vs reference", gk)
 
 
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 256, 8, 16), (1, 1500, 4, 8), (2, 300, 24, 16)], ids=lambda s: "B%dT%dD%dN%d" % s)
+def test_entry_points_on_the_reference_kernels_own_buffers(cuda_dev, rk, shape, dt):
+    """mamba_b200_ssm_scan_bwd reads the block-boundary rows straight out of the h_saved the
+    REFERENCE's saving forward wrote, and out of the sparse h_saved this library's
+    mamba_b200_ssm_scan_fwd_save writes: both must give the reference backward's gradients."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, T, D, N = shape
+    q = m1_case(B, T, D, N, dt, seed=T + 3 * N)
+    td = torch_dtype(dt)
+    d = lambda a, t_=None: to_dev(a, cuda_dev, t_)
+    delta, u, Bm, Cm, dy = (d(q[k], td) for k in ("delta", "u", "Bm", "Cm", "dy"))
+    a_neg, Dp = d(q["a_neg"]), d(q["Dp"])
+    h_ref, y_ref = d(q["h0"]), torch.empty(B, T, D, device=cuda_dev, dtype=td)
+    hs_ref = torch.empty(B, T + 1, D, N, device=cuda_dev)
+    rk.ssm_parallel_scan_fwd(dt, h_ref, y_ref, hs_ref, delta, u, Bm, Cm, a_neg, Dp)
+    ref = rk.ssm_scan_bwd("parallel", dt, hs_ref, delta, u, Bm, Cm, a_neg, Dp, dy)
+    h_lib, y_lib = d(q["h0"]), torch.empty(B, T, D, device=cuda_dev, dtype=td)
+    hs_lib = torch.full((B, T + 1, D, N), float("nan"), device=cuda_dev)
+    mb.ssm_scan_fwd_save(h_lib, y_lib, hs_lib, delta, u, Bm, Cm, a_neg, Dp)
+    g_on_ref = mb.ssm_scan_bwd(hs_ref, delta, u, Bm, Cm, a_neg, Dp, dy)
+    g_on_lib = mb.ssm_scan_bwd(hs_lib, delta, u, Bm, Cm, a_neg, Dp, dy)
+    torch.cuda.synchronize()
+    tol = TOL[dt]
+    assert rel_err(host(y_lib), host(y_ref)) <= tol
+    assert rel_err(host(h_lib), host(h_ref)) <= 1e-4
+    rows = list(range(0, T, 32))
+    assert rel_err(host(hs_lib[:, rows]), host(hs_ref[:, rows])) <= 1e-4   # the rows that are written
+    assert bool(torch.isnan(hs_lib[:, 1]).all())                          # and nothing else
+    for g in (g_on_ref, g_on_lib):
+        for k in ("d_delta", "d_u", "dB", "dC", "dD", "dA_log"):
+            assert rel_err(host(g[k]), host(ref[k])) <= tol, k
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_conv_nosave_entry_point_on_the_reference_argument_list(cuda_dev, rk, dt):
+    import torch
+
+    import mamba_rs_b200 as mb
+    B, T, D, K = 2, 130, 40, 4
+    rng = np.random.default_rng(5)
+    x = synth.round_to(rng.standard_normal((B, T, D)).astype(np.float32), dt)
+    w = rng.uniform(-0.8, 0.8, (D, K)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(D)).astype(np.float32)
+    st0 = rng.standard_normal((B, D, K)).astype(np.float32)
+    td = torch_dtype(dt)
+    d = lambda a, t_=None: to_dev(a, cuda_dev, t_)
+    st_ref, u_ref = d(st0), torch.empty(B, T, D, device=cuda_dev, dtype=td)
+    rk.conv1d_burnin_forward_nosave(dt, u_ref, st_ref, d(x, td), d(w), d(bias))
+    st_lib, u_lib = d(st0), torch.empty(B, T, D, device=cuda_dev, dtype=td)
+    mb.conv1d_fwd_nosave(u_lib, st_lib, d(x, td), d(w), d(bias))
+    torch.cuda.synchronize()
+    assert rel_err(host(u_lib), host(u_ref)) <= TOL[dt]
+    np.testing.assert_array_equal(host(st_lib), host(st_ref))
+
+
 @pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("shape", [(2, 150, 40, 4), (1, 700, 24, 4), (3, 64, 8, 2)],
                          ids=lambda s: "B%dT%dD%dK%d" % s)
