@@ -32,6 +32,13 @@
 
 namespace mb200 {
 
+// m1_bwd_wide.cu: 16 < d_state <= 256
+int bwd_wide_lpc(int N);
+size_t bwd_wide_smem(int N, int S);
+cudaError_t bwd_wide_configure();
+cudaError_t launch_bwd_wide(const BwdParams& p, int dtype, int softplus, cudaStream_t st, int* tiles);
+
+
 constexpr int kBwdSub = 16;   // sub-block length (h_t kept in shared memory)
 constexpr int kBwdSMax = 64;  // largest save_stride
 
@@ -537,11 +544,6 @@ int m1_bwd_configure(Ctx* c) {
 
 static int bwd_ns(int N) { return N <= 4 ? 4 : (N <= 8 ? 8 : 16); }
 
-// m1_bwd_wide.cu: 16 < d_state <= 256
-int bwd_wide_lpc(int N);
-size_t bwd_wide_smem(int N, int S);
-cudaError_t bwd_wide_configure();
-cudaError_t launch_bwd_wide(const BwdParams& p, int dtype, int softplus, cudaStream_t st, int* tiles);
 
 static void bwd_ws_layout(int B, int T, int D, int N, size_t* off_a, size_t* off_d, size_t* off_dense,
                           size_t* total) {
