@@ -48,7 +48,8 @@ def test_forward_backward_conv_and_step_replay_bit_identically_from_a_graph(cuda
 
     def snapshot():
         torch.cuda.synchronize()
-        keep = dict(y=y, u=u, ssm=ssm, cst=cst, ys=ys, dA=dA, dD=dD, dW=dW, db=db, **out)
+        keep = dict(out)
+        keep.update(y=y, u=u, ssm=ssm, cst=cst, ys=ys, dA=dA, dD=dD, dW=dW, db=db)
         return {k: v.float().cpu().numpy().copy() for k, v in keep.items() if v is not None}
 
     layer()  # eager (also makes every first-call set-up happen outside the capture)
