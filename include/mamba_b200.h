@@ -407,6 +407,60 @@ MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream, const mamba
 MAMBA_B200_API long long mamba_b200_conv1d_bwd_static_max_bytes(void);
 MAMBA_B200_API int mamba_b200_conv1d_bwd_static(void* handle, void* stream, const mamba_b200_conv1d_args* args);
 
+/*
+ * Residual add + RMSNorm in one pass, forward and backward.  Between two layers the
+ * reference launches residual_add_f32_{dt} (kernels/elementwise.cu:367-377; f32
+ * residual stream += the 16-bit out_proj output) and then rmsnorm_forward_f32in_{dt}
+ * (kernels/norms.cu:126-168) on the stream it has just written
+ * (src/mamba_ssm/gpu/forward_mixed.rs:433-480, :745-758).
+ *   forward : residual [rows, dim] f32 += branch [rows, dim] (storage dtype; NULL = no
+ *             add); y [rows, dim] (storage dtype) = residual / rms * scale; rms_out [rows]
+ *             (NULL = not kept) is what the backward needs.  rms = sqrt(mean(x^2) + eps),
+ *             replaced by 1 when it is not finite (the reference's guard).
+ *   backward: replaces rmsnorm_backward_f32in_{dt} (kernels/norms.cu:323-367), the
+ *             [rows, dim] d_scale partials and their reduce_sum_axis0, and the add of dx
+ *             into the residual gradient: d_residual [rows, dim] f32 += dx;
+ *             d_scale [dim] f32 += sum over rows (per-CTA partials in the workspace,
+ *             added in CTA order: no atomics).  x is the residual the forward normalised.
+ * dim <= 16384.
+ */
+MAMBA_B200_API int mamba_b200_residual_rmsnorm_fwd(void* handle, void* stream, int dtype, float* residual,
+                                    const void* branch, const float* scale, void* y, float* rms_out,
+                                    int rows, int dim, float eps);
+MAMBA_B200_API long long mamba_b200_residual_rmsnorm_bwd_workspace_bytes(int rows, int dim);
+MAMBA_B200_API int mamba_b200_residual_rmsnorm_bwd(void* handle, void* stream, int dtype, const void* dy,
+                                    const float* x, const float* scale, const float* rms_saved,
+                                    float* d_residual, float* d_scale, int rows, int dim, void* workspace,
+                                    long long workspace_bytes);
+
+/*
+ * The ends of a training step on the device.  The reference trainer receives its input
+ * rows and the output gradient from the host (src/mamba_ssm/gpu/trainer.rs:437-481) and
+ * its language-model wrapper keeps a [vocab, d_model] table for both the embedding and
+ * the tied head (src/module/gpu_lm.rs:560-679); these three launches have no kernel
+ * counterpart there except AdamW.
+ *   embedding_gather: out [rows, dim] f32 (the residual stream) = table[ids[r], :]
+ *             (table in the storage dtype; an id outside [0, vocab) gives a zero row).
+ *   softmax_xent    : per row of logits [rows, ld] (V used columns, storage dtype):
+ *             loss_rows[r] = logsumexp(l) - l[target]; with d_logits != NULL also
+ *             d_logits = (softmax(l) - onehot(target)) * grad_scale.  target < 0 marks a
+ *             row that does not count (loss 0, zero gradient).  One read of the logits,
+ *             one write of the gradient when a row fits shared memory (V * size <= 208 KB).
+ *   adamw_step      : adamw_step_f32_capturable (kernels/adamw.cu:30-61; decoupled decay,
+ *             bias_factors = {1/(1-beta1^t), 1/(1-beta2^t)} in a 2-float DEVICE buffer so the
+ *             launch can sit in a captured graph) fused with the reference's separate
+ *             master -> compute cast (trainer.rs:1453-1475): param_lp (f16 / bf16, may be
+ *             NULL) receives the updated parameter in the compute dtype.
+ */
+MAMBA_B200_API int mamba_b200_embedding_gather(void* handle, void* stream, int dtype, const void* table,
+                                const int* ids, float* out, long long rows, int dim, int vocab);
+MAMBA_B200_API int mamba_b200_softmax_xent(void* handle, void* stream, int dtype, const void* logits,
+                            const int* targets, float* loss_rows, void* dlogits, float grad_scale,
+                            long long rows, int V, long long ld);
+MAMBA_B200_API int mamba_b200_adamw_step(void* handle, void* stream, float* param, const float* grad, float* m,
+                          float* v, float lr, float beta1, float beta2, float eps, float weight_decay,
+                          const float* bias_factors, void* param_lp, int lp_dtype, long long n);
+
 #ifdef __cplusplus
 }
 #endif

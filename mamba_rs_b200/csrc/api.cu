@@ -43,6 +43,8 @@ int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limit
 int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
 int m3_configure(Ctx* c);       // m3_ssd.cu
 int m3_bwd_configure(Ctx* c);   // m3_ssd_bwd.cu
+int norm_configure(Ctx* c);     // norm.cu
+int train_ops_configure(Ctx* c);  // train_ops.cu
 
 }  // namespace mb200
 
@@ -79,6 +81,10 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     rc = m3_configure(c);
     if (rc) return rc;
     rc = m3_bwd_configure(c);
+    if (rc) return rc;
+    rc = norm_configure(c);
+    if (rc) return rc;
+    rc = train_ops_configure(c);
     if (rc) return rc;
     return MAMBA_B200_OK;
 }

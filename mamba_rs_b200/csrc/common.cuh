@@ -49,6 +49,24 @@ __device__ __forceinline__ void st_pair(__half* p, float2 v) {
     *reinterpret_cast<__half2*>(p) = __float22half2_rn(v);
 }
 
+// Two f32 values <-> one 32-bit word of two 16-bit storage elements.
+template <typename Th> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename Th> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+
 // ---- math conventions -------------------------------------------------------
 // exp2 on the MUFU pipe (2 ulp); every exp of the path is exp2(x * log2 e), the
 // convention of the reference's device code (kernels/_typed_prelude.cuh:20-32).

@@ -104,23 +104,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-template <typename Th> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-template <typename Th> __device__ __forceinline__ float2 unpack2(uint32_t w);
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
-    return __half22float2(*reinterpret_cast<__half2*>(&w));
-}
-
 // Byte offset of the 16-byte chunk (row r, 8-column group j) in a tile of C columns.
 __device__ __forceinline__ uint32_t chunk_off(int r, int j, int C) {
     return static_cast<uint32_t>((r >> 3) * (C >> 3) * 128 + j * 128 + (r & 7) * 16);

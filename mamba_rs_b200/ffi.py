@@ -148,6 +148,13 @@ def lib() -> C.CDLL:
         bind("mamba_b200_conv1d_bwd_workspace_bytes", [C.c_int] * 4, C.c_longlong)
         bind("mamba_b200_conv1d_bwd_static", [vp, vp, C.POINTER(Conv1dArgs)])
         bind("mamba_b200_conv1d_bwd_static_max_bytes", [], C.c_longlong)
+        ll, fl, it = C.c_longlong, C.c_float, C.c_int
+        bind("mamba_b200_residual_rmsnorm_fwd", [vp, vp, it, vp, vp, vp, vp, vp, it, it, fl])
+        bind("mamba_b200_residual_rmsnorm_bwd_workspace_bytes", [it, it], ll)
+        bind("mamba_b200_residual_rmsnorm_bwd", [vp, vp, it, vp, vp, vp, vp, vp, vp, it, it, vp, ll])
+        bind("mamba_b200_embedding_gather", [vp, vp, it, vp, vp, vp, ll, it, it])
+        bind("mamba_b200_softmax_xent", [vp, vp, it, vp, vp, vp, vp, fl, ll, it, ll])
+        bind("mamba_b200_adamw_step", [vp, vp, vp, vp, vp, vp, fl, fl, fl, fl, fl, vp, vp, it, ll])
         bind("mamba_b200_m3_ssd_fwd", [vp, vp, C.POINTER(M3SsdArgs)])
         bind("mamba_b200_m3_ssd_bwd", [vp, vp, C.POINTER(M3SsdBwdArgs)])
         bind("mamba_b200_m3_ssd_bwd_workspace_bytes", [C.c_int] * 5, C.c_longlong)

@@ -17,6 +17,7 @@ from . import ffi
 
 __all__ = ["selective_scan_fwd", "selective_scan_fwd_workspace_bytes", "selective_scan_bwd",
            "selective_scan_bwd_workspace_bytes",
+           "residual_rmsnorm_fwd", "residual_rmsnorm_bwd", "embedding_gather", "softmax_xent", "adamw_step",
            "ssm_parallel_scan_fwd_nosave", "ssm_scan_fwd_save", "ssm_scan_bwd", "conv1d_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
 
 
@@ -406,3 +407,102 @@ def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy, *, dD=None, workspace=None, handl
         rc = ffi.lib().mamba_b200_m3_ssd_bwd(h.ptr, _stream(dev), C.byref(a))
     h.check(rc, "mamba_b200_m3_ssd_bwd")
     return dict(dx=dx, dK=dK, dQ=dQ, d_adt=d_adt, d_dt=d_dt, d_trap=d_trap, dD=dD)
+
+
+def residual_rmsnorm_fwd(residual, branch, scale, *, eps=1e-5, out_dtype=None, y=None, rms_out=None, handle=None):
+    """residual [rows, dim] f32 += branch (storage dtype, or None); returns
+    (y = rmsnorm(residual) * scale in the storage dtype, rms [rows] f32)."""
+    _require_cuda(residual, branch, scale, y, rms_out)
+    rows, dim = residual.shape
+    dev = residual.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or not scale.is_contiguous():
+        raise TypeError("residual and scale are contiguous float32")
+    dt = branch.dtype if branch is not None else (out_dtype or torch.bfloat16)
+    if branch is not None and (not branch.is_contiguous() or tuple(branch.shape) != (rows, dim)):
+        raise ValueError("branch must be contiguous [rows, dim]")
+    if y is None:
+        y = torch.empty((rows, dim), dtype=dt, device=dev)
+    if rms_out is None:
+        rms_out = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_residual_rmsnorm_fwd(h.ptr, _stream(dev), dtype_code(dt), _ptr(residual), _ptr(branch),
+                                                       _ptr(scale), _ptr(y), _ptr(rms_out), rows, dim, float(eps))
+    h.check(rc, "mamba_b200_residual_rmsnorm_fwd")
+    return y, rms_out
+
+
+def residual_rmsnorm_bwd(dy, x, scale, rms_saved, d_residual, d_scale, *, workspace=None, handle=None):
+    """d_residual [rows, dim] f32 += dx of the RMSNorm; d_scale [dim] f32 += its scale
+    gradient.  x is the f32 residual the forward normalised, rms_saved its per-row rms."""
+    _require_cuda(dy, x, scale, rms_saved, d_residual, d_scale, workspace)
+    rows, dim = x.shape
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    need = int(ffi.lib().mamba_b200_residual_rmsnorm_bwd_workspace_bytes(rows, dim))
+    if workspace is None:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_residual_rmsnorm_bwd(h.ptr, _stream(dev), dtype_code(dy.dtype), _ptr(dy), _ptr(x),
+                                                       _ptr(scale), _ptr(rms_saved), _ptr(d_residual), _ptr(d_scale),
+                                                       rows, dim, _ptr(workspace), workspace.numel())
+    h.check(rc, "mamba_b200_residual_rmsnorm_bwd")
+    return d_residual, d_scale
+
+
+def embedding_gather(table, ids, out=None, *, handle=None):
+    """out [rows, dim] f32 = table[ids] (table [vocab, dim] in the storage dtype, ids int32)."""
+    _require_cuda(table, ids, out)
+    vocab, dim = table.shape
+    dev = table.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    ids = ids.reshape(-1)
+    if ids.dtype != torch.int32 or not ids.is_contiguous() or not table.is_contiguous():
+        raise TypeError("ids are contiguous int32, the table is contiguous")
+    if out is None:
+        out = torch.empty((ids.numel(), dim), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_embedding_gather(h.ptr, _stream(dev), dtype_code(table.dtype), _ptr(table), _ptr(ids),
+                                                   _ptr(out), ids.numel(), dim, vocab)
+    h.check(rc, "mamba_b200_embedding_gather")
+    return out
+
+
+def softmax_xent(logits, targets, *, grad_scale=1.0, want_grad=True, dlogits=None, handle=None):
+    """Per-row cross-entropy of logits [rows, V] against int32 targets (negative = not
+    counted).  Returns (loss_rows f32 [rows], d_logits in the logits' dtype or None)."""
+    _require_cuda(logits, targets, dlogits)
+    rows, V = logits.shape
+    dev = logits.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    if logits.stride(1) != 1 or targets.dtype != torch.int32 or not targets.is_contiguous():
+        raise TypeError("logits rows are contiguous, targets are contiguous int32")
+    loss = torch.empty(rows, dtype=torch.float32, device=dev)
+    if want_grad and dlogits is None:
+        dlogits = torch.empty_strided(logits.shape, logits.stride(), dtype=logits.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_softmax_xent(h.ptr, _stream(dev), dtype_code(logits.dtype), _ptr(logits), _ptr(targets),
+                                               _ptr(loss), _ptr(dlogits if want_grad else None), float(grad_scale),
+                                               rows, V, logits.stride(0))
+    h.check(rc, "mamba_b200_softmax_xent")
+    return loss, (dlogits if want_grad else None)
+
+
+def adamw_step(param, grad, m, v, bias_factors, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0,
+               param_lp=None, handle=None):
+    """In-place AdamW on flat f32 arenas; bias_factors is a 2-float device tensor
+    {1/(1-beta1^t), 1/(1-beta2^t)}; param_lp (f16 / bf16) receives the compute copy."""
+    _require_cuda(param, grad, m, v, bias_factors, param_lp)
+    dev = param.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    for t in (param, grad, m, v, bias_factors):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError("AdamW state is contiguous float32")
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_adamw_step(h.ptr, _stream(dev), _ptr(param), _ptr(grad), _ptr(m), _ptr(v), float(lr),
+                                             float(beta1), float(beta2), float(eps), float(weight_decay),
+                                             _ptr(bias_factors), _ptr(param_lp),
+                                             dtype_code(param_lp.dtype) if param_lp is not None else ffi.BF16,
+                                             param.numel())
+    h.check(rc, "mamba_b200_adamw_step")
+    return param

@@ -376,3 +376,58 @@ def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy):
                          *[_p(out[k]) for k in ("dx", "dK", "dQ", "d_alpha", "d_beta", "d_gamma", "d_adt",
                                                 "d_dt", "d_trap", "dD")])
     return out
+
+
+# -- the rows around the scan: residual + RMSNorm, loss, optimiser (numpy) -----------
+
+def residual_rmsnorm_fwd(residual, branch, scale, eps=1e-5):
+    """residual_add_f32_{dt} (kernels/elementwise.cu:367-377) followed by
+    rmsnorm_forward_f32in_{dt} (kernels/norms.cu:126-168), in f32: returns the new
+    residual, y = x / rms * scale, and rms = sqrt(mean(x^2) + eps) per row."""
+    x = np.asarray(residual, np.float32)
+    if branch is not None:
+        x = (x + np.asarray(branch, np.float32)).astype(np.float32)
+    rms = np.sqrt((x.astype(np.float64) ** 2).mean(axis=1) + eps).astype(np.float32)
+    rms = np.where(np.isfinite(rms) & (rms >= 1e-20), rms, np.float32(1.0))
+    y = x * (np.float32(1.0) / rms)[:, None] * np.asarray(scale, np.float32)[None, :]
+    return x, y.astype(np.float32), rms
+
+
+def residual_rmsnorm_bwd(dy, x, scale, rms):
+    """rmsnorm_backward (kernels/norms.cu:181-240): dx = (scale*dy - x_hat*mean(dy*y_hat)) /
+    rms; d_scale = sum over rows of dy * x_hat.  f64 arithmetic."""
+    dy, x, scale, rms = (np.asarray(a, np.float64) for a in (dy, x, scale, rms))
+    inv = 1.0 / rms[:, None]
+    xh = x * inv
+    mean = (dy * xh * scale[None, :]).mean(axis=1, keepdims=True)
+    dx = (scale[None, :] * dy - xh * mean) * inv
+    return dx, (dy * xh).sum(axis=0)
+
+
+def softmax_xent(logits, targets, grad_scale=1.0):
+    """Cross-entropy per row and its gradient (softmax - onehot) * grad_scale; rows with a
+    negative target do not count.  f64 arithmetic."""
+    l = np.asarray(logits, np.float64)
+    m = l.max(axis=1, keepdims=True)
+    e = np.exp(l - m)
+    S = e.sum(axis=1, keepdims=True)
+    counted = np.asarray(targets) >= 0
+    tsafe = np.where(counted, targets, 0)
+    loss = (m[:, 0] + np.log(S[:, 0])) - l[np.arange(l.shape[0]), tsafe]
+    g = e / S
+    g[np.arange(l.shape[0]), tsafe] -= 1.0
+    g *= grad_scale
+    g[~counted] = 0.0
+    return np.where(counted, loss, 0.0), g
+
+
+def adamw_step(param, grad, m, v, lr, beta1, beta2, eps, wd, step):
+    """adamw_step_f32 (kernels/adamw.cu:63-95) in f32, the reference's operation order."""
+    f = np.float32
+    p, g, m, v = (np.asarray(a, f).copy() for a in (param, grad, m, v))
+    bc1 = f(1.0 / (1.0 - beta1 ** step))
+    bc2 = f(1.0 / (1.0 - beta2 ** step))
+    m = m * f(beta1) + f(1.0 - f(beta1)) * g
+    v = v * f(beta2) + f(1.0 - f(beta2)) * g * g
+    p = f(1.0 - f(lr) * f(wd)) * p - f(lr) * (m * bc1) / (np.sqrt(v * bc2) + f(eps))
+    return p.astype(f), m.astype(f), v.astype(f), (bc1, bc2)
