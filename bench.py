@@ -52,7 +52,8 @@ WORKLOAD = dict(B=16, T=2048, D=1536, N=16, dtype="bf16")
 METRIC = "selective_scan_fwd_algorithmic_GBps"
 FALLBACK_HBM_GBS = 6650.0
 OPS = ["sscan_fwd", "sscan_fwd_random_a", "sscan_fwd_unfused", "sscan_fwd_small_batch", "sscan_bwd", "conv1d_fwd",
-       "conv1d_bwd", "sscan_step", "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd"]
+       "conv1d_bwd", "sscan_step", "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd", "residual_rmsnorm_fwd",
+       "residual_rmsnorm_bwd", "softmax_xent", "adamw_step", "embedding_gather"]
 
 
 def measured_peaks():
@@ -262,6 +263,43 @@ def op_case(name, dev, batch=0, save_stride=32, heads=32, headdim=64, dstate=128
         # x, K, Q, dy read; dx written; dK, dQ f32; five [B,T,nh] f32 vectors
         by = (3 * e * B * T * nh * hd + 2 * e * B * T * nh * N + 2 * 4 * B * T * nh * N + 6 * 4 * B * T * nh)
         return (lambda: mb.m3_ssd_bwd(*a, dy, workspace=ws)), by, cfg
+
+    if name in ("residual_rmsnorm_fwd", "residual_rmsnorm_bwd", "embedding_gather"):
+        rows, dim = (batch or 8) * 8192, 2560  # the 2.8b layer shape: one GPU's shard of tokens
+        cfg = dict(rows=rows, dim=dim, storage="bf16")
+        scale = torch.ones(dim, device=dev)
+        res = torch.randn(rows, dim, device=dev)
+        if name == "embedding_gather":
+            V = 50280
+            table = torch.randn(V, dim, device=dev).to(bf)
+            ids = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+            cfg["vocab"] = V
+            return (lambda: mb.embedding_gather(table, ids, res)), rows * dim * (e + 4) + 4 * rows, cfg
+        if name == "residual_rmsnorm_fwd":
+            br = torch.randn(rows, dim, device=dev).to(bf)
+            y, rms = torch.empty_like(br), torch.empty(rows, device=dev)
+            return (lambda: mb.residual_rmsnorm_fwd(res, br, scale, y=y, rms_out=rms)), rows * dim * 2 * (4 + e), cfg
+        dy = torch.randn(rows, dim, device=dev).to(bf)
+        rms = res.pow(2).mean(1).add(1e-5).sqrt()
+        dres, dsc = torch.zeros(rows, dim, device=dev), torch.zeros(dim, device=dev)
+        ws = torch.empty(int(mb.ffi.lib().mamba_b200_residual_rmsnorm_bwd_workspace_bytes(rows, dim)), dtype=torch.uint8,
+                         device=dev)
+        return (lambda: mb.residual_rmsnorm_bwd(dy, res, scale, rms, dres, dsc, workspace=ws)), rows * dim * (e + 12), cfg
+    if name == "softmax_xent":
+        rows, V = (batch or 1) * 8192, 50280
+        lg = (3.0 * torch.randn(rows, V, device=dev)).to(bf)
+        tg = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+        dlg = torch.empty_like(lg)
+        cfg = dict(rows=rows, vocab=V, storage="bf16")
+        return (lambda: mb.softmax_xent(lg, tg, dlogits=dlg)), rows * V * 2 * e + 8 * rows, cfg
+    if name == "adamw_step":
+        n = 100_000_000
+        pa, g, m, v = (torch.randn(n, device=dev) for _ in range(4))
+        v.abs_()
+        lp = torch.empty(n, device=dev, dtype=bf)
+        bcf = torch.tensor([1.1, 1.2], device=dev)
+        cfg = dict(params=n, compute_copy="bf16")
+        return (lambda: mb.adamw_step(pa, g, m, v, bcf, lr=1e-4, weight_decay=0.1, param_lp=lp)), n * (16 + 12 + e), cfg
 
     small = name == "sscan_fwd_small_batch"
     B = batch or (8 if name in ("sscan_step", "decode_loop") else (1 if small else 16))
@@ -654,7 +692,8 @@ def main():
         if world == 1:
             extra = {}
             for name in ("sscan_fwd_random_a", "sscan_bwd", "conv1d_fwd", "conv1d_bwd", "sscan_fwd_small_batch",
-                         "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd"):
+                         "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd", "residual_rmsnorm_fwd", "residual_rmsnorm_bwd",
+                         "softmax_xent", "adamw_step", "embedding_gather"):
                 r = measure_op(name, dev)
                 r.pop("op")
                 extra[name] = r

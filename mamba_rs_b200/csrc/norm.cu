@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_fwd_kernel(cons
 // dx = (scale * dy - x_hat * mean(dy * y_hat)) / rms, added into d_residual;
 // d_scale[i] += sum over rows of dy * x_hat (per-CTA partial, reduced afterwards in
 // CTA order).
-template <typename Tact>
+template <typename Tact, bool VEC>
 __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_bwd_kernel(const NormParams p) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[kNormThreads / 32];
@@ -131,17 +131,55 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_bwd_kernel(cons
     for (long long r = blockIdx.x; r < p.rows; r += gridDim.x) {
         const float inv = 1.0f / p.rms_saved[r];
         float s = 0.0f;
-        for (int i = tid; i < dim; i += kNormThreads) {
-            const float xv = p.x[r * dim + i] * inv, g = to_f(dy[r * dim + i]);
-            xh[i] = xv;
-            dyv[i] = g;
-            s = fmaf(g, xv * p.scale[i], s);
+        if (VEC) {
+            for (int i = tid * 4; i < dim; i += kNormThreads * 4) {
+                float4 xv = *reinterpret_cast<const float4*>(p.x + r * dim + i);
+                xv.x *= inv; xv.y *= inv; xv.z *= inv; xv.w *= inv;
+                float4 g;
+                if constexpr (sizeof(Tact) == 2) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(dy + r * dim + i);
+                    const float2 lo = unpack2<Tact>(raw.x), hi = unpack2<Tact>(raw.y);
+                    g = make_float4(lo.x, lo.y, hi.x, hi.y);
+                } else {
+                    g = *reinterpret_cast<const float4*>(dy + r * dim + i);
+                }
+                const float4 sc = *reinterpret_cast<const float4*>(p.scale + i);
+                *reinterpret_cast<float4*>(xh + i) = xv;
+                *reinterpret_cast<float4*>(dyv + i) = g;
+                s = fmaf(g.x, xv.x * sc.x, s);
+                s = fmaf(g.y, xv.y * sc.y, s);
+                s = fmaf(g.z, xv.z * sc.z, s);
+                s = fmaf(g.w, xv.w * sc.w, s);
+            }
+        } else {
+            for (int i = tid; i < dim; i += kNormThreads) {
+                const float xv = p.x[r * dim + i] * inv, g = to_f(dy[r * dim + i]);
+                xh[i] = xv;
+                dyv[i] = g;
+                s = fmaf(g, xv * p.scale[i], s);
+            }
         }
         const float mean = block_sum(s, red) / static_cast<float>(dim);
-        for (int i = tid; i < dim; i += kNormThreads) {
-            const float xv = xh[i], g = dyv[i];
-            p.d_residual[r * dim + i] += (p.scale[i] * g - xv * mean) * inv;
-            acc[i] = fmaf(g, xv, acc[i]);  // element i is always this thread's
+        if (VEC) {
+            for (int i = tid * 4; i < dim; i += kNormThreads * 4) {
+                const float4 xv = *reinterpret_cast<const float4*>(xh + i), g = *reinterpret_cast<const float4*>(dyv + i);
+                const float4 sc = *reinterpret_cast<const float4*>(p.scale + i);
+                float4 dr = *reinterpret_cast<const float4*>(p.d_residual + r * dim + i);
+                dr.x += (sc.x * g.x - xv.x * mean) * inv;
+                dr.y += (sc.y * g.y - xv.y * mean) * inv;
+                dr.z += (sc.z * g.z - xv.z * mean) * inv;
+                dr.w += (sc.w * g.w - xv.w * mean) * inv;
+                *reinterpret_cast<float4*>(p.d_residual + r * dim + i) = dr;
+                float4 a = *reinterpret_cast<const float4*>(acc + i);  // elements i..i+3 are always this thread's
+                a.x = fmaf(g.x, xv.x, a.x); a.y = fmaf(g.y, xv.y, a.y); a.z = fmaf(g.z, xv.z, a.z); a.w = fmaf(g.w, xv.w, a.w);
+                *reinterpret_cast<float4*>(acc + i) = a;
+            }
+        } else {
+            for (int i = tid; i < dim; i += kNormThreads) {
+                const float xv = xh[i], g = dyv[i];
+                p.d_residual[r * dim + i] += (p.scale[i] * g - xv * mean) * inv;
+                acc[i] = fmaf(g, xv, acc[i]);  // element i is always this thread's
+            }
         }
         __syncthreads();
     }
@@ -164,9 +202,12 @@ static int norm_ctas(const Ctx* c, int rows) {
 
 int norm_configure(Ctx* c) {
     const int lim = 3 * kNormMaxDim * 4;
-    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_bwd_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     const int limf = kNormMaxDim * 4;
     MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_fwd_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limf));
     MB200_CUDA_CHECK(c, cudaFuncSetAttribute(residual_rmsnorm_fwd_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limf));
@@ -245,9 +286,17 @@ extern "C" MAMBA_B200_API int mamba_b200_residual_rmsnorm_bwd(void* handle, void
     p.rows = rows; p.dim = dim;
     const size_t smem = sizeof(float) * 3 * dim;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == MAMBA_B200_F32) residual_rmsnorm_bwd_kernel<float><<<grid, kNormThreads, smem, st>>>(p);
-    else if (dtype == MAMBA_B200_F16) residual_rmsnorm_bwd_kernel<__half><<<grid, kNormThreads, smem, st>>>(p);
-    else residual_rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, kNormThreads, smem, st>>>(p);
+    auto al = [](const void* q, size_t a) { return reinterpret_cast<uintptr_t>(q) % a == 0; };
+    const bool vec = dim % 4 == 0 && al(x, 16) && al(scale, 16) && al(d_residual, 16) && al(dy, 4 * dtype_size(dtype));
+#define MB200_NORM_BWD(T)                                                                        \
+    do {                                                                                         \
+        if (vec) residual_rmsnorm_bwd_kernel<T, true><<<grid, kNormThreads, smem, st>>>(p);      \
+        else residual_rmsnorm_bwd_kernel<T, false><<<grid, kNormThreads, smem, st>>>(p);         \
+    } while (0)
+    if (dtype == MAMBA_B200_F32) MB200_NORM_BWD(float);
+    else if (dtype == MAMBA_B200_F16) MB200_NORM_BWD(__half);
+    else MB200_NORM_BWD(__nv_bfloat16);
+#undef MB200_NORM_BWD
     MB200_CUDA_CHECK(c, cudaGetLastError());
     norm_dscale_reduce_kernel<<<(dim + 255) / 256, 256, 0, st>>>(p.part, d_scale, grid, dim);
     MB200_CUDA_CHECK(c, cudaGetLastError());
