@@ -409,6 +409,67 @@ def run_op(args):
     print(json.dumps(out))
 
 
+def lm_extra(dev, world, rank):
+    """Model-level figures through the host-side engines (library GEMMs between this
+    library's kernels), per rank on its own sequences, max over ranks:
+      * 130m architecture (d_model 768, 24 layers, vocab 50280, tied head), random init,
+        bf16: prefill of 8 x 2048 token ids, then 128 greedy decode steps (CUDA graph);
+      * 2.8b layer shape (d_model 2560, d_inner 5120, dt_rank 160, vocab 50280), bf16
+        compute / f32 master, 4 of its 64 layers, 2 x 8192 tokens per micro-batch: one
+        training step (forward, cross-entropy, backward, bucketed all-reduce under the
+        backward when N > 1, AdamW)."""
+    import torch
+    import torch.distributed as dist
+
+    import mamba_rs_b200 as mb
+
+    def tmax(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    # ---- 130m: prefill + decode ----
+    cfg = mb.MambaConfig(d_model=768, n_layers=24)
+    V, B, T, steps = 50280, 8, 2048, 128
+    w = mb.MambaWeights(cfg, dev, dtype=torch.bfloat16, vocab=V).init_random(0)
+    ids = torch.randint(0, V, (B, T), device=dev, dtype=torch.int32, generator=g)
+    lm = mb.GpuMambaLM(w, B)
+
+    def prefill():
+        lm.backbone.reset()
+        lm.prefill(ids)
+    ms_prefill = tmax(time_call(prefill, 5, 2))
+    lm.generate_greedy(2)  # builds the graph
+    ms_decode = tmax(time_call(lambda: lm.generate_greedy(steps), 3, 1))
+    out["lm_130m"] = {"config": "d_model 768, 24 layers, d_state 16, vocab 50280, tied head, bf16, random init seed 0",
+                      "prefill": {"batch": B, "seq_len": T, "ms": ms_prefill,
+                                  "tokens_per_s": world * B * T / (ms_prefill * 1e-3)},
+                      "decode": {"batch": B, "steps": steps, "ms": ms_decode, "cuda_graph": True,
+                                 "tokens_per_s": world * B * steps / (ms_decode * 1e-3),
+                                 "ms_per_step": ms_decode / steps}}
+    del lm, w
+    torch.cuda.empty_cache()
+    # ---- 2.8b layer shape: training step ----
+    L = 4
+    cfg = mb.MambaConfig(d_model=2560, n_layers=L)
+    Bm, Tm = 2, 8192
+    w = mb.MambaWeights(cfg, dev, dtype=torch.bfloat16, vocab=V).init_random(3)
+    tr = mb.MambaLMTrainer(w)
+    tok = torch.randint(0, V, (Bm, Tm + 1), device=dev, dtype=torch.int32, generator=g)
+    ms_train = tmax(time_call(lambda: tr.step(tok), 3, 1))
+    out["lm_2p8b_train_step"] = {
+        "config": f"d_model 2560, d_inner 5120, dt_rank 160, d_state 16, vocab 50280, {L} of 64 layers, bf16 compute / "
+                  "f32 master, random init seed 3",
+        "micro_batch": Bm, "seq_len": Tm, "ms": ms_train, "tokens_per_s": world * Bm * Tm / (ms_train * 1e-3),
+        "parameters": int(w.n), "allreduce": "bucketed per layer under the backward" if world > 1 else "single rank"}
+    del tr, w
+    torch.cuda.empty_cache()
+    return out
+
+
 def collective_extra(dev, world, rank):
     """The one collective of the design, measured: all-reduce (sum) of a flat f32
     gradient arena, bucketed per layer, alone and issued on a side stream while the scan
@@ -700,6 +761,7 @@ def main():
         else:
             c = collective_extra(dev, world, rank)
             extra = {"gradient_allreduce": c}
+        extra.update(lm_extra(dev, world, rank))
 
     if rank == 0:
         by = algorithmic_bytes(w)

@@ -11,4 +11,4 @@ from . import ffi  # noqa: F401
 from .ffi import Handle, LibraryMissing, lib, lib_path  # noqa: F401
 from .ops import *  # noqa: F401,F403
 from .parallel import BucketedGradReducer, allreduce_grads, shard_batch  # noqa: F401,E402
-from .model import GpuMambaBackbone, MambaConfig, MambaLMTrainer, MambaWeights  # noqa: F401,E402
+from .model import GpuMambaBackbone, GpuMambaLM, MambaConfig, MambaLMTrainer, MambaWeights  # noqa: F401,E402

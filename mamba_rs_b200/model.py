@@ -28,7 +28,7 @@ import torch
 from . import ops
 from .parallel import BucketedGradReducer
 
-__all__ = ["MambaConfig", "MambaWeights", "GpuMambaBackbone", "MambaLMTrainer"]
+__all__ = ["MambaConfig", "MambaWeights", "GpuMambaBackbone", "GpuMambaLM", "MambaLMTrainer"]
 
 
 @dataclass
@@ -231,6 +231,67 @@ class GpuMambaBackbone:
                                         self.ssm[l], proj[:, di:])
             branch = y @ p["out_proj_w"]
         out, _ = ops.residual_rmsnorm_fwd(res, branch, w.tail("master")["norm_f"], eps=c.rms_norm_eps, out_dtype=w.dtype)
+        return out
+
+
+class GpuMambaLM:
+    """Token-level wrapper with a tied head (``GpuMambaLM``, src/module/gpu_lm.rs:136-679):
+    ``prefill`` runs whole prompts through the backbone and returns the logits of the last
+    position, ``generate_greedy`` decodes token by token.  One decode step (embedding row,
+    24-layer step, head GEMM, argmax) is captured in a CUDA graph on first use and replayed,
+    as the reference captures its step (src/mamba_ssm/gpu/inference.rs:1608-1630)."""
+
+    def __init__(self, weights: MambaWeights, batch: int):
+        if not weights.vocab:
+            raise ValueError("the LM needs weights with a vocabulary")
+        self.w, self.batch = weights, batch
+        self.backbone = GpuMambaBackbone(weights, batch)
+        dev = weights.device
+        self.next_ids = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.logits = torch.empty(batch, weights.vocab, device=dev, dtype=weights.dtype)
+        self._graph = None
+
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [B, T] int32 -> logits of the last position [B, vocab]; leaves the greedy
+        next token in ``next_ids``."""
+        B, T = ids.shape
+        emb = self.w.tail()["embedding"]
+        temporal = ops.embedding_gather(emb, ids.contiguous()).view(B, T, -1)
+        hidden = self.backbone.prefill_sequence(temporal)
+        torch.matmul(hidden[:, -1], emb.t(), out=self.logits)
+        self.next_ids.copy_(self.logits.argmax(dim=1))
+        return self.logits
+
+    def _decode_once(self):
+        emb = self.w.tail()["embedding"]
+        temporal = ops.embedding_gather(emb, self.next_ids)
+        hidden = self.backbone.step(temporal)
+        torch.matmul(hidden, emb.t(), out=self.logits)
+        self.next_ids.copy_(self.logits.argmax(dim=1))
+
+    def generate_greedy(self, n: int, use_graph: bool = True) -> torch.Tensor:
+        """n greedy tokens after a prefill; returns them as [B, n] int32."""
+        out = torch.empty(self.batch, n, dtype=torch.int32, device=self.w.device)
+        if use_graph and self._graph is None:
+            dev = self.w.device
+            keep = (self.backbone.conv.clone(), self.backbone.ssm.clone(), self.next_ids.clone())
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                self._decode_once()  # warm-up outside the capture (first-call set-up, cuBLAS workspaces)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._decode_once()
+            self.backbone.conv.copy_(keep[0])
+            self.backbone.ssm.copy_(keep[1])
+            self.next_ids.copy_(keep[2])
+        for i in range(n):
+            out[:, i] = self.next_ids
+            if use_graph:
+                self._graph.replay()
+            else:
+                self._decode_once()
         return out
 
 

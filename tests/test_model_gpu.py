@@ -153,3 +153,21 @@ def test_bf16_training_step_runs_at_a_model_layer_shape(cuda_dev):
     torch.cuda.synchronize()
     assert abs(float(loss) - np.log(V)) < 0.5
     assert bool(torch.isfinite(w.grad).all()) and float(w.grad.abs().max()) > 0
+
+
+def test_greedy_decode_from_a_captured_graph_equals_eager_decode(cuda_dev):
+    import torch
+
+    import mamba_rs_b200 as mb
+    cfg = mb.MambaConfig(d_model=128, n_layers=3)
+    V, B, T, n = 997, 4, 60, 12
+    w = mb.MambaWeights(cfg, cuda_dev, dtype=torch.bfloat16, vocab=V).init_random(11)
+    ids = torch.randint(0, V, (B, T), device=cuda_dev, dtype=torch.int32,
+                        generator=torch.Generator(device=cuda_dev).manual_seed(2))
+    outs = []
+    for use_graph in (False, True):
+        lm = mb.GpuMambaLM(w, B)
+        lm.prefill(ids)
+        outs.append(lm.generate_greedy(n, use_graph=use_graph).cpu().numpy())
+    np.testing.assert_array_equal(outs[0], outs[1])
+    assert outs[0].min() >= 0 and outs[0].max() < V
