@@ -363,18 +363,44 @@ __global__ void __launch_bounds__(32) sscan_bwd_kernel(const __grid_constant__ B
 }
 
 // dB / dC: add the channel tiles in index order.  part [B][tiles][T][2N] -> dB, dC [B,T,N].
-__global__ void bwd_reduce_bc_kernel(const float* __restrict__ part, float* __restrict__ dB,
-                                     float* __restrict__ dC, int B, int T, int N, int NSv, int tiles) {
+// A thread owns four adjacent values of one (sample, step) and keeps eight 16-byte
+// loads in flight; the sum still runs in tile order.
+__global__ void __launch_bounds__(256) bwd_reduce_bc_kernel(const float* __restrict__ part, float* __restrict__ dB,
+                                                            float* __restrict__ dC, int B, int T, int N, int NSv,
+                                                            int tiles, int vec_out) {
     const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const int V = 2 * NSv;
-    if (i >= static_cast<long long>(B) * T * V) return;
-    const int v = i % V;
-    const long long bt = i / V;
+    const int V = 2 * NSv, V4 = V / 4;
+    if (i >= static_cast<long long>(B) * T * V4) return;
+    const int v = static_cast<int>(i % V4) * 4;
+    const long long bt = i / V4;
     const long long bb = bt / T, t = bt % T;
-    float acc = 0.0f;
-    for (int k = 0; k < tiles; ++k) acc += part[((bb * tiles + k) * T + t) * V + v];
+    const long long stride = static_cast<long long>(T) * V;
+    const float* src = part + (bb * tiles * T + t) * V + v;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    int k = 0;
+    for (; k + 8 <= tiles; k += 8) {
+        float4 q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = __ldcs(reinterpret_cast<const float4*>(src + (k + j) * stride));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            acc.x += q[j].x; acc.y += q[j].y; acc.z += q[j].z; acc.w += q[j].w;
+        }
+    }
+    for (; k < tiles; ++k) {
+        const float4 q = __ldcs(reinterpret_cast<const float4*>(src + k * stride));
+        acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+    float* dst = v < NSv ? dB : dC;
     const int n = v % NSv;
-    if (n < N) (v < NSv ? dB : dC)[bt * N + n] = acc;
+    const float out[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (vec_out && n + 3 < N) {
+        *reinterpret_cast<float4*>(dst + bt * N + n) = acc;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (n + j < N) dst[bt * N + n + j] = out[j];
+    }
 }
 
 // dA_log[D,N] += sum_b part_a, dD[D] += sum_b part_d, in sample order
@@ -616,6 +642,7 @@ static int launch_bwd(Ctx* c, void* stream, const mamba_b200_sscan_bwd_args& a, 
     p.cs_ld_b = cs_ld_b ? cs_ld_b : p.cs_ld_k * ((a.T + a.save_stride - 1) / a.save_stride);
     unsigned char* ws = static_cast<unsigned char*>(a.workspace);
     p.part_bc = reinterpret_cast<float*>(ws);
+    const int bc_vec = a.N % 4 == 0 && (reinterpret_cast<uintptr_t>(a.dBm) | reinterpret_cast<uintptr_t>(a.dCm)) % 16 == 0;
     p.part_a = reinterpret_cast<float*>(ws + off_a);
     p.part_d = reinterpret_cast<float*>(ws + off_d);
     p.B = a.B; p.T = a.T; p.D = a.D; p.N = a.N; p.S = a.save_stride; p.z_mode = a.z_mode;
@@ -629,9 +656,9 @@ static int launch_bwd(Ctx* c, void* stream, const mamba_b200_sscan_bwd_args& a, 
         cudaError_t e = launch_bwd_wide(p, a.dtype, a.delta_softplus, stw, &wtiles);
         if (e != cudaSuccess) return fail(c, MAMBA_B200_ERR_CUDA, "sscan_bwd (wide): %s", cudaGetErrorString(e));
         const int np = 8 * bwd_wide_lpc(a.N);
-        const long long nbcw = static_cast<long long>(a.B) * a.T * 2 * np;
+        const long long nbcw = static_cast<long long>(a.B) * a.T * 2 * np / 4;
         bwd_reduce_bc_kernel<<<static_cast<unsigned>((nbcw + 255) / 256), 256, 0, stw>>>(
-            p.part_bc, a.dBm, a.dCm, a.B, a.T, a.N, np, wtiles);
+            p.part_bc, a.dBm, a.dCm, a.B, a.T, a.N, np, wtiles, bc_vec);
         MB200_CUDA_CHECK(c, cudaGetLastError());
         const int npar = a.D * a.N;
         bwd_reduce_params_kernel<<<(npar + 255) / 256, 256, 0, stw>>>(p.part_a, p.part_d, a.dA_log, a.dD, a.B, a.D,
@@ -683,9 +710,9 @@ static int launch_bwd(Ctx* c, void* stream, const mamba_b200_sscan_bwd_args& a, 
         t.fn[a.dtype][vi][flags]<<<grid, 32, t.smem[a.dtype][vi], st>>>(p);
     }
     MB200_CUDA_CHECK(c, cudaGetLastError());
-    const long long nbc = static_cast<long long>(a.B) * a.T * 2 * ns;
+    const long long nbc = static_cast<long long>(a.B) * a.T * 2 * ns / 4;
     bwd_reduce_bc_kernel<<<static_cast<unsigned>((nbc + 255) / 256), 256, 0, st>>>(
-        p.part_bc, a.dBm, a.dCm, a.B, a.T, a.N, ns, tiles);
+        p.part_bc, a.dBm, a.dCm, a.B, a.T, a.N, ns, tiles, bc_vec);
     MB200_CUDA_CHECK(c, cudaGetLastError());
     const int np = a.D * a.N;
     bwd_reduce_params_kernel<<<(np + 255) / 256, 256, 0, st>>>(p.part_a, p.part_d, a.dA_log, a.dD, a.B,
