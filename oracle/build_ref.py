@@ -5,7 +5,7 @@ with NVRTC at run time (src/mamba_ssm/gpu/kernels.rs:451-545, options
 --fmad=true --extra-device-vectorization); here nvcc does the same offline for
 sm_100a.  No reference source is copied into this repository.
 
-    python oracle/build_ref.py [/path/to/mamba-rs]
+    python oracle/build_ref.py /path/to/mamba-rs      (or MAMBA_RS_REFERENCE=/path/to/mamba-rs)
 """
 import os
 import subprocess
@@ -13,15 +13,18 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = "/root/reference"
+ENV_REF = "MAMBA_RS_REFERENCE"
 FILES = ["mamba_ssm_parallel.cu", "mamba_ssm.cu", "conv1d.cu", "mamba3_chunked.cu", "mamba3_ssd.cu"]
 
 
-def build_ref(ref_root: str = DEFAULT_REF, verbose: bool = False) -> bool:
+def build_ref(ref_root: str = "", verbose: bool = False) -> bool:
+    """ref_root: the mounted mamba-rs tree; empty = the MAMBA_RS_REFERENCE environment
+    variable; nothing is built when neither names a tree."""
+    ref_root = ref_root or os.environ.get(ENV_REF, "")
     kdir = os.path.join(ref_root, "kernels")
-    if not os.path.isdir(kdir):
+    if not ref_root or not os.path.isdir(kdir):
         if verbose:
-            print(f"no reference tree at {ref_root}: oracle/_ref not built")
+            print(f"no reference tree at {ref_root!r}: oracle/_ref not built")
         return False
     os.makedirs(OUT, exist_ok=True)
     procs = []
@@ -46,5 +49,5 @@ def build_ref(ref_root: str = DEFAULT_REF, verbose: bool = False) -> bool:
 
 
 if __name__ == "__main__":
-    build_ref(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF, verbose=True)
+    build_ref(sys.argv[1] if len(sys.argv) > 1 else "", verbose=True)
     print(sorted(os.listdir(OUT)) if os.path.isdir(OUT) else "nothing built")

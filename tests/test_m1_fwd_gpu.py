@@ -223,7 +223,7 @@ def test_argument_errors_are_reported_not_launched(cuda_dev):
 
 
 def test_full_size_linearity_and_split_at_config2(cuda_dev):
-    """BASELINE config #2 (B=16, D=1536, N=16, L=2048, bf16) is too large for the
+    """The benchmark shape (B=16, D=1536, N=16, L=2048, bf16) is too large for the
     CPU oracle in a unit test; check size-independent properties instead:
     (1) with z fixed the op is linear in u: f(2u) == 2 f(u) up to bf16 rounding,
     (2) two half-length calls with the state carried == one call,

@@ -166,7 +166,7 @@ def test_backward_matches_f64_finite_differences():
         assert abs(fd - an) <= 5e-3 * max(abs(fd), abs(an)) + 2e-5, ("a_log", idx, fd, an)
 
 
-# --- BASELINE config #1: backbone prefill, batch == per-sample, taps feed the fused op ---
+# --- d_model 128 x 2 layers, B 4 x T 512: backbone prefill, batch == per-sample, taps feed the fused op ---
 
 def test_backbone_prefill_config1_consistency():
     cfg = oracle.m1_config(d_model=128, n_layers=2, d_state=16, d_conv=4, expand=2, input_dim=128)
