@@ -52,7 +52,7 @@ WORKLOAD = dict(B=16, T=2048, D=1536, N=16, dtype="bf16")
 METRIC = "selective_scan_fwd_algorithmic_GBps"
 FALLBACK_HBM_GBS = 6650.0
 OPS = ["sscan_fwd", "sscan_fwd_random_a", "sscan_fwd_unfused", "sscan_fwd_small_batch", "sscan_bwd", "conv1d_fwd",
-       "conv1d_bwd", "sscan_step", "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd", "residual_rmsnorm_fwd",
+       "conv1d_bwd", "sscan_step", "decode_loop", "m3_ssd_fwd", "m3_ssd_fwd_fused_kq", "m3_ssd_bwd", "residual_rmsnorm_fwd",
        "residual_rmsnorm_bwd", "softmax_xent", "adamw_step", "embedding_gather"]
 
 
@@ -252,6 +252,17 @@ def op_case(name, dev, batch=0, save_stride=32, heads=32, headdim=64, dstate=128
         i = synth.m3_ssd_inputs(B, T, nh, hd, N, seed=0)
         a = [t(i[k], bf if k in ("x", "K", "Q") else None) for k in ("x", "K", "Q", "dt", "trap", "adt", "Dh")]
         cfg = dict(B=B, T=T, nh=nh, hd=hd, N=N, storage="bf16")
+        if name == "m3_ssd_fwd_fused_kq":
+            ng, na = 1, N // 4  # one group, rope_fraction 0.5 (the reference's default)
+            g = synth.m3_group_inputs(B, T, nh, ng, N, na, i["dt"], seed=0)
+            y = torch.empty_like(a[0])
+            ssm = torch.zeros(B, nh, hd, N, device=dev)
+            ang = t(g["angle_state"])
+            ga = [t(g["Bn"], bf), t(g["Cn"], bf), t(g["b_bias"]), t(g["c_bias"]), t(g["angle_vel"])]
+            cfg.update(ngroups=ng, n_angles=na)
+            by = synth.m3_fused_kq_algorithmic_bytes(B, T, nh, ng, hd, N, na, e)
+            return (lambda: mb.m3_ssd_fwd_fused_kq(a[0], *ga, a[3], a[4], a[5], a[6], angle_state=ang,
+                                                   ssm_state=ssm, y=y)), by, cfg
         if name == "m3_ssd_fwd":
             y = torch.empty_like(a[0])
             ssm = torch.zeros(B, nh, hd, N, device=dev)
@@ -753,8 +764,8 @@ def main():
         if world == 1:
             extra = {}
             for name in ("sscan_fwd_random_a", "sscan_bwd", "conv1d_fwd", "conv1d_bwd", "sscan_fwd_small_batch",
-                         "decode_loop", "m3_ssd_fwd", "m3_ssd_bwd", "residual_rmsnorm_fwd", "residual_rmsnorm_bwd",
-                         "softmax_xent", "adamw_step", "embedding_gather"):
+                         "decode_loop", "m3_ssd_fwd", "m3_ssd_fwd_fused_kq", "m3_ssd_bwd", "residual_rmsnorm_fwd",
+                         "residual_rmsnorm_bwd", "softmax_xent", "adamw_step", "embedding_gather"):
                 r = measure_op(name, dev)
                 r.pop("op")
                 extra[name] = r

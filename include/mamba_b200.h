@@ -330,6 +330,28 @@ typedef struct mamba_b200_m3_ssd_args {
     float* v_state;
     int carry_in;         /* 1: continue from the given state (sequential kernel) */
     int force_sequential; /* 1: never take the tensor-core path (for comparison) */
+    /* Optional (Bn != NULL; tensor-core path only, else MAMBA_B200_ERR_SHAPE): the per-head
+     * K and Q are built inside the kernel and K, Q above are ignored.  Replaces
+     * bc_bias_add (kernels/mamba3_ops.cu:279-310), m3_angle_dt_fwd_seq (:400-440) and
+     * rope_fwd (:575-640) and the two [B,T,nh,N] tensors they write
+     * (src/mamba3_siso/cpu/forward.rs:336-375 is the definition):
+     *   K[t,h,:] = rope(Bn[t,g,:] + b_bias[h,:], angle[t,h,:]), g = h / (nh / ng); Q from Cn, c_bias
+     *   angle[t,h,a] = (angle_state[h,a] + sum_{s<=t} angle_vel[s,a] * dt[s,h]) mod 2 pi
+     *   rope rotates the pairs (2a, 2a+1), a < n_angles; the other columns pass through.
+     * Bn, Cn [B,T,ng,N] storage dtype (after BCNorm); b_bias, c_bias [nh,N] f32;
+     * angle_vel [B,T,n_angles] f32 = tanh(angles_raw) * pi (the head-independent factor the
+     * reference hoists, forward.rs:318-325); angle_state [B,nh,n_angles] f32, read and
+     * overwritten with the angle after the window (NULL: zero in, not written).
+     * n_angles a multiple of 4, 2 * n_angles <= N.  The in-chunk sums run in f32, the
+     * angle entering each 128-step chunk is carried in f64. */
+    const void* Bn;
+    const void* Cn;
+    const float* b_bias;
+    const float* c_bias;
+    const float* angle_vel;
+    float* angle_state;
+    int ng;
+    int n_angles;
 } mamba_b200_m3_ssd_args;
 
 MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream, const mamba_b200_m3_ssd_args* args);

@@ -28,6 +28,13 @@ struct M3Params {
     float *ssm_state, *k_state, *v_state;  // in/out (may be null: zero in, not written)
     int B, T, nh, hd, N;
     int carry_in;  // 1: the state buffers hold a state to continue from
+    // Optional: K and Q built inside the tensor-core kernel from the group-level
+    // B / C after BCNorm, the per-head biases and RoPE (Bn == nullptr: K, Q are read).
+    const void *Bn, *Cn;            // [B,T,ng,N] storage dtype
+    const float *b_bias, *c_bias;   // [nh,N]
+    const float* angle_vel;         // [B,T,n_angles]: tanh(angles_raw) * pi
+    float* angle_state;             // [B,nh,n_angles] in/out (may be null: zero in, not written)
+    int ng, n_angles;
     int* status;
 };
 
@@ -123,13 +130,24 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // that holds w o V for the state update and then the 16-bit copy of the new
 // state for the next chunk's Y2; then f32 vectors, barriers.
 constexpr uint32_t kQ = 0, kM = 0, kK = 32768, kV = 65536, kVw = 81920, kS = 81920;
-constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128]
-constexpr uint32_t kBar = kVec + 4 * 128 * 4, kTmemSlot = kBar + 16;
+constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128]
+// K / Q generation: per-warp angle totals [4][64], entering angle f32 [64] and f64 [64],
+// this head's B / C biases [2][128]
+constexpr uint32_t kWtot = kVec + 5 * 128 * 4, kBase = kWtot + 4 * 64 * 4, kCarry = kBase + 64 * 4,
+                   kBias = kCarry + 64 * 8;
+constexpr uint32_t kBar = kBias + 2 * 128 * 4, kTmemSlot = kBar + 16;
 constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
 constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
 
-template <typename Th>
+// GEN: build the K and Q tiles of a chunk in the kernel instead of reading them:
+//   K[t,h,:] = rope(Bn[t,g,:] + b_bias[h,:], angle[t,h,:]),  Q likewise from Cn / c_bias,
+//   angle[t,h,a] = (angle_in[h,a] + sum_{s<=t} angle_vel[s,a] * dt[s,h]) mod 2 pi
+// (src/mamba3_siso/cpu/forward.rs:336-375; kernels/mamba3_ops.cu:279-310, :400-440,
+// :575-640).  Thread (row, half) owns the 16-byte pieces j = half, half + 2, ... of its
+// row; the in-chunk sums run as shuffle scans over the rows, the angle entering a chunk
+// is carried in f64.
+template <typename Th, bool GEN>
 __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // two threads per step: thread (row, half) owns row `row` of the chunk (TMEM lane
@@ -151,6 +169,22 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         fence_barrier_init();
+    }
+    float* dtv = vec + 512;
+    float* wtot = reinterpret_cast<float*>(smem + kWtot);
+    float* basef = reinterpret_cast<float*>(smem + kBase);
+    double* carry = reinterpret_cast<double*>(smem + kCarry);
+    float* bias_sm = reinterpret_cast<float*>(smem + kBias);
+    if (GEN) {
+        if (threadIdx.x < 64) {
+            const int a = threadIdx.x;
+            const float v = (a < p.n_angles && p.angle_state)
+                                ? p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + a] : 0.0f;
+            carry[a] = static_cast<double>(v);
+            basef[a] = v;
+        }
+        const float* bsrc = half ? p.c_bias : p.b_bias;
+        bias_sm[half * 128 + tid] = tid < nsv ? bsrc[static_cast<long long>(h) * nsv + tid] : 0.0f;
     }
     if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tslot)),
@@ -207,11 +241,12 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         float* scl = dA + 128;
         float* gam = dA + 256;
         const int t0 = c * CS, nv = min(CS, T - t0), t = t0 + tid;
-        float a = 0.0f, g = 0.0f, s = 0.0f;
+        float a = 0.0f, g = 0.0f, s = 0.0f, dtr = 0.0f;
         if (tid < nv) {
             const long long th = (static_cast<long long>(b) * T + t) * nh + h;
             a = p.adt[th];
-            g = p.dt[th] * p.trap[th];
+            dtr = p.dt[th];
+            g = dtr * p.trap[th];
             s = g;
             if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
         }
@@ -224,6 +259,7 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         if (lane == 31) dA[warp] = run;  // slot reused below after the barrier
         gam[tid] = g;
         scl[tid] = s;
+        if (GEN) dA[512 + tid] = dtr;
         __syncthreads();
         float off = 0.0f;
         for (int w = 0; w < warp; ++w) off += dA[w];
@@ -231,6 +267,108 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         dA[tid] = run + off;
         dA[384 + tid] = (run + off) * kLog2e;
         __syncthreads();
+    };
+
+
+    // K and Q tiles of chunk c from the group-level rows (GEN only).
+    auto gen_qk = [&](int c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const bool rok = tid < nv;
+        const long long bt = static_cast<long long>(b) * T + t0 + (rok ? tid : 0);
+        const int na = p.n_angles;
+        constexpr double kTwoPi64 = 6.283185307179586;
+        // the angle entering this chunk: previous entering angle + the previous chunk's sums
+        if (c > 0 && threadIdx.x < na) {
+            const int a = threadIdx.x;
+            double sacc = carry[a] + (static_cast<double>(wtot[a]) + static_cast<double>(wtot[64 + a]) +
+                                      static_cast<double>(wtot[128 + a]) + static_cast<double>(wtot[192 + a]));
+            sacc -= kTwoPi64 * floor(sacc / kTwoPi64);
+            carry[a] = sacc;
+            basef[a] = static_cast<float>(sacc);
+        }
+        // angle increments of this row, then the inclusive sums over the rows of the warp
+        const float dtr = rok ? dtv[tid] : 0.0f;
+        float cum[8][4];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int j = 2 * k + half;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (4 * j < na && rok) v = __ldg(reinterpret_cast<const float4*>(p.angle_vel + bt * na + 4 * j));
+            cum[k][0] = v.x * dtr; cum[k][1] = v.y * dtr; cum[k][2] = v.z * dtr; cum[k][3] = v.w * dtr;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (4 * (2 * k + half) < na) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = cum[k][e];
+#pragma unroll
+                    for (int m = 1; m < 32; m <<= 1) {
+                        const float o = __shfl_up_sync(0xffffffffu, v, m);
+                        if (lane >= m) v += o;
+                    }
+                    cum[k][e] = v;
+                }
+            }
+        }
+        __syncthreads();  // the previous totals have been folded into the entering angle
+        if (lane == 31) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (4 * (2 * k + half) < na) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) wtot[warp * 64 + 4 * (2 * k + half) + e] = cum[k][e];
+                }
+        }
+        __syncthreads();
+        const Th* Bg = static_cast<const Th*>(p.Bn);
+        const Th* Cg = static_cast<const Th*>(p.Cn);
+        const int grp = h / (nh / p.ng);
+        const long long rowoff = (bt * p.ng + grp) * nsv;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int j = 2 * k + half;
+            uint4 ko = make_uint4(0, 0, 0, 0), qo = ko;
+            if (8 * j < nsv && rok) {
+                const uint4 braw = __ldg(reinterpret_cast<const uint4*>(Bg + rowoff + 8 * j));
+                const uint4 craw = __ldg(reinterpret_cast<const uint4*>(Cg + rowoff + 8 * j));
+                const uint32_t bw[4] = {braw.x, braw.y, braw.z, braw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w};
+                const float4 bb0 = *reinterpret_cast<const float4*>(bias_sm + 8 * j);
+                const float4 bb1 = *reinterpret_cast<const float4*>(bias_sm + 8 * j + 4);
+                const float4 cb0 = *reinterpret_cast<const float4*>(bias_sm + 128 + 8 * j);
+                const float4 cb1 = *reinterpret_cast<const float4*>(bias_sm + 128 + 8 * j + 4);
+                const float bbv[8] = {bb0.x, bb0.y, bb0.z, bb0.w, bb1.x, bb1.y, bb1.z, bb1.w};
+                const float cbv[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
+                uint32_t kw[4], qw[4];
+                const bool rot = 4 * j < na;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 bf = unpack2<Th>(bw[e]), cf = unpack2<Th>(cw[e]);
+                    float k0 = bf.x + bbv[2 * e], k1 = bf.y + bbv[2 * e + 1];
+                    float q0 = cf.x + cbv[2 * e], q1 = cf.y + cbv[2 * e + 1];
+                    if (rot) {
+                        const int a = 4 * j + e;
+                        float ang = basef[a] + cum[k][e];
+                        for (int w = 0; w < warp; ++w) ang += wtot[w * 64 + a];
+                        // to [-pi, pi] before the fast sine / cosine
+                        const float turns = rintf(ang * 0.15915494309189535f);
+                        ang = fmaf(turns, -6.2831854820251465f, ang);
+                        ang = fmaf(turns, 1.7484555e-7f, ang);
+                        float sn, cs;
+                        __sincosf(ang, &sn, &cs);
+                        const float rk0 = cs * k0 - sn * k1, rk1 = sn * k0 + cs * k1;
+                        const float rq0 = cs * q0 - sn * q1, rq1 = sn * q0 + cs * q1;
+                        k0 = rk0; k1 = rk1; q0 = rq0; q1 = rq1;
+                    }
+                    kw[e] = pack2<Th>(k0, k1);
+                    qw[e] = pack2<Th>(q0, q1);
+                }
+                ko = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+                qo = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+            }
+            *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = ko;
+            *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = qo;
+        }
     };
 
     for (int c = 0; c < nchunks; ++c) {
@@ -242,11 +380,14 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         const float* gam = dA + 256;
         const uint32_t tK = kK, tV = kV;
         // ---- 1. this chunk's Q, K, V tiles (asynchronous copies) and per-row scalars ----
-        issue_qk(Qg, kQ, c);
-        issue_qk(Kg, kK, c);
+        if (!GEN) {
+            issue_qk(Qg, kQ, c);
+            issue_qk(Kg, kK, c);
+        }
         issue_v(kV, c);
         asm volatile("cp.async.commit_group;" ::: "memory");
         scalars(c, 0);
+        if (GEN) gen_qk(c);
         asm volatile("cp.async.wait_all;" ::: "memory");
         fence_proxy_async();
         fence_before();
@@ -398,7 +539,21 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
         const long long last = static_cast<long long>(b) * T + (T - 1);
-        if (p.k_state && half == 0 && tid < nsv)
+        if (GEN) {
+            // the last K row is still in its tile; fold the last chunk's sums into the angle
+            const int lr = T - 1 - (nchunks - 1) * CS;
+            if (p.k_state && half == 0 && tid < nsv)
+                p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] =
+                    to_f(*reinterpret_cast<const Th*>(smem + kK + chunk_off(lr, tid >> 3, NS) + (tid & 7) * 2));
+            if (p.angle_state && threadIdx.x < p.n_angles) {
+                const int a = threadIdx.x;
+                constexpr double kTwoPi64 = 6.283185307179586;
+                double sacc = carry[a] + (static_cast<double>(wtot[a]) + static_cast<double>(wtot[64 + a]) +
+                                          static_cast<double>(wtot[128 + a]) + static_cast<double>(wtot[192 + a]));
+                sacc -= kTwoPi64 * floor(sacc / kTwoPi64);
+                p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + a] = static_cast<float>(sacc);
+            }
+        } else if (p.k_state && half == 0 && tid < nsv)
             p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] = to_f(Kg[(last * nh + h) * nsv + tid]);
         if (p.v_state && half == 0 && tid < hdv)
             p.v_state[(static_cast<long long>(b) * nh + h) * hdv + tid] = to_f(xg[last * nh * hdv + h * hdv + tid]);
@@ -412,10 +567,12 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
 }  // namespace tc
 
 int m3_configure(Ctx* c) {
-    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16>),
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem));
-    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__half>),
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem));
+    const void* fns[4] = {reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, false>),
+                          reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__half, false>),
+                          reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, true>),
+                          reinterpret_cast<const void*>(tc::m3_ssd_fwd_tc_kernel<__half, true>)};
+    for (const void* fn : fns)
+        MB200_CUDA_CHECK(c, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem));
     return MAMBA_B200_OK;
 }
 
@@ -447,8 +604,18 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
         return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: headdim %d > 1024 or d_state %d > 128", a.hd, a.N);
     if (a.B == 0 || a.T == 0) return MAMBA_B200_OK;
     if (a.B > 65535) return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: batch %d > 65535", a.B);
-    if (!a.x || !a.K || !a.Q || !a.dt || !a.trap || !a.adt || !a.Dh || !a.y)
+    const bool gen = a.Bn != nullptr;
+    if (!a.x || (!gen && (!a.K || !a.Q)) || !a.dt || !a.trap || !a.adt || !a.Dh || !a.y)
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: null required pointer");
+    if (gen) {
+        if (!a.Cn || !a.b_bias || !a.c_bias || a.ng <= 0 || a.nh % a.ng != 0 || a.n_angles < 0 ||
+            (a.n_angles > 0 && !a.angle_vel))
+            return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: K/Q generation needs Bn, Cn, both biases, ngroups "
+                                                "dividing nheads and angle_vel when n_angles > 0");
+        if (a.n_angles % 4 != 0 || 2 * a.n_angles > a.N)
+            return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: n_angles %d must be a multiple of 4 and <= d_state / 2",
+                        a.n_angles);
+    }
     if (a.carry_in && (!a.ssm_state || !a.k_state || !a.v_state))
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_fwd: carry_in needs all three state buffers");
     M3Params p;
@@ -456,18 +623,28 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
     p.x = a.x; p.K = a.K; p.Q = a.Q; p.dt = a.dt; p.trap = a.trap; p.adt = a.adt; p.Dh = a.Dh; p.y = a.y;
     p.ssm_state = a.ssm_state; p.k_state = a.k_state; p.v_state = a.v_state;
     p.B = a.B; p.T = a.T; p.nh = a.nh; p.hd = a.hd; p.N = a.N; p.carry_in = a.carry_in;
+    p.Bn = a.Bn; p.Cn = a.Cn; p.b_bias = a.b_bias; p.c_bias = a.c_bias; p.angle_vel = a.angle_vel;
+    p.angle_state = a.angle_state; p.ng = a.ng; p.n_angles = a.n_angles;
     p.status = c->d_status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd <= tc::HD && a.hd % 8 == 0 && a.N <= tc::NS &&
                              a.N % 8 == 0 && !a.carry_in &&
-                             !a.force_sequential && al16(a.x) && al16(a.K) && al16(a.Q) && al16(a.y);
+                             !a.force_sequential && al16(a.x) && al16(a.y) &&
+                             (gen ? al16(a.Bn) && al16(a.Cn) && al16(a.angle_vel) : al16(a.K) && al16(a.Q));
+    if (gen && !tensor_core)
+        return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: K/Q generation runs on the tensor-core path only (16-bit "
+                                              "storage, headdim <= 64, d_state <= 128, multiples of 8, no carried "
+                                              "state, 16-byte aligned tensors)");
     if (tensor_core) {
         dim3 grid(a.nh, a.B);
-        if (a.dtype == MAMBA_B200_BF16)
-            tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16><<<grid, 256, tc::kSmem, st>>>(p);
-        else
-            tc::m3_ssd_fwd_tc_kernel<__half><<<grid, 256, tc::kSmem, st>>>(p);
+        if (a.dtype == MAMBA_B200_BF16) {
+            if (gen) tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, true><<<grid, 256, tc::kSmem, st>>>(p);
+            else tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, false><<<grid, 256, tc::kSmem, st>>>(p);
+        } else {
+            if (gen) tc::m3_ssd_fwd_tc_kernel<__half, true><<<grid, 256, tc::kSmem, st>>>(p);
+            else tc::m3_ssd_fwd_tc_kernel<__half, false><<<grid, 256, tc::kSmem, st>>>(p);
+        }
     } else {
         if (a.dtype == MAMBA_B200_F32) launch_seq<float>(p, st);
         else if (a.dtype == MAMBA_B200_F16) launch_seq<__half>(p, st);

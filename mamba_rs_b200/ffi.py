@@ -91,6 +91,8 @@ class M3SsdArgs(C.Structure):
         ("y", C.c_void_p),
         ("ssm_state", C.c_void_p), ("k_state", C.c_void_p), ("v_state", C.c_void_p),
         ("carry_in", C.c_int), ("force_sequential", C.c_int),
+        ("Bn", C.c_void_p), ("Cn", C.c_void_p), ("b_bias", C.c_void_p), ("c_bias", C.c_void_p),
+        ("angle_vel", C.c_void_p), ("angle_state", C.c_void_p), ("ng", C.c_int), ("n_angles", C.c_int),
     ]
 
 

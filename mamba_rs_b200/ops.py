@@ -18,7 +18,7 @@ from . import ffi
 __all__ = ["selective_scan_fwd", "selective_scan_fwd_workspace_bytes", "selective_scan_bwd",
            "selective_scan_bwd_workspace_bytes",
            "residual_rmsnorm_fwd", "residual_rmsnorm_bwd", "embedding_gather", "softmax_xent", "adamw_step",
-           "ssm_parallel_scan_fwd_nosave", "ssm_scan_fwd_save", "ssm_scan_bwd", "conv1d_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_bwd", "dtype_code"]
+           "ssm_parallel_scan_fwd_nosave", "ssm_scan_fwd_save", "ssm_scan_bwd", "conv1d_fwd_nosave", "selective_scan_step", "conv1d_fwd", "conv1d_bwd", "m3_ssd_fwd", "m3_ssd_fwd_fused_kq", "m3_ssd_bwd", "dtype_code"]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -361,6 +361,46 @@ def m3_ssd_fwd(x, K, Q, dt, trap, adt, Dh, *, ssm_state=None, k_state=None, v_st
     a.y = _ptr(y)
     a.ssm_state, a.k_state, a.v_state = _ptr(ssm_state), _ptr(k_state), _ptr(v_state)
     a.carry_in, a.force_sequential = int(carry_in), int(force_sequential)
+    with torch.cuda.device(dev):
+        rc = ffi.lib().mamba_b200_m3_ssd_fwd(h.ptr, _stream(dev), C.byref(a))
+    h.check(rc, "mamba_b200_m3_ssd_fwd")
+    return y
+
+
+def m3_ssd_fwd_fused_kq(x, Bn, Cn, b_bias, c_bias, angle_vel, dt, trap, adt, Dh, *, angle_state=None,
+                        ssm_state=None, k_state=None, v_state=None, y=None, handle=None):
+    """Mamba-3 SISO SSD forward with the per-head K / Q built inside the kernel (bias add +
+    RoPE with the running angle) from the group-level rows.  x [B,T,nh*hd], Bn / Cn
+    [B,T,ng,N] in the 16-bit storage dtype; b_bias, c_bias [nh,N], angle_vel [B,T,n_angles]
+    (= tanh(angles_raw) * pi; None = no rotation), dt, trap, adt [B,T,nh], Dh [nh] f32;
+    angle_state [B,nh,n_angles] f32 is read and overwritten with the angle after the window."""
+    _require_cuda(x, Bn, Cn, b_bias, c_bias, angle_vel, dt, trap, adt, Dh, angle_state, ssm_state, k_state,
+                  v_state, y)
+    Bsz, T, ng, N = Bn.shape
+    nh = b_bias.shape[0]
+    hd = x.shape[2] // nh
+    dev = x.device
+    h = handle or ffi.default_handle(dev.index or 0)
+    for t, nm in ((x, "x"), (Bn, "Bn"), (Cn, "Cn")):
+        if not t.is_contiguous() or t.dtype != x.dtype:
+            raise ValueError(f"{nm} must be contiguous and share x's dtype")
+    for t, nm in ((b_bias, "b_bias"), (c_bias, "c_bias"), (angle_vel, "angle_vel"), (dt, "dt"), (trap, "trap"),
+                  (adt, "adt"), (Dh, "Dh"), (angle_state, "angle_state"), (ssm_state, "ssm_state"),
+                  (k_state, "k_state"), (v_state, "v_state")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError(f"{nm} must be contiguous float32")
+    if y is None:
+        y = torch.empty_like(x)
+    a = ffi.M3SsdArgs()
+    a.dtype = dtype_code(x.dtype)
+    a.B, a.T, a.nh, a.hd, a.N = Bsz, T, nh, hd, N
+    a.x = _ptr(x)
+    a.dt, a.trap, a.adt, a.Dh = _ptr(dt), _ptr(trap), _ptr(adt), _ptr(Dh)
+    a.y = _ptr(y)
+    a.ssm_state, a.k_state, a.v_state = _ptr(ssm_state), _ptr(k_state), _ptr(v_state)
+    a.Bn, a.Cn, a.b_bias, a.c_bias = _ptr(Bn), _ptr(Cn), _ptr(b_bias), _ptr(c_bias)
+    a.angle_vel, a.angle_state = _ptr(angle_vel), _ptr(angle_state)
+    a.ng, a.n_angles = ng, (angle_vel.shape[2] if angle_vel is not None else 0)
     with torch.cuda.device(dev):
         rc = ffi.lib().mamba_b200_m3_ssd_fwd(h.ptr, _stream(dev), C.byref(a))
     h.check(rc, "mamba_b200_m3_ssd_fwd")

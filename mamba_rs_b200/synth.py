@@ -88,6 +88,30 @@ def m3_ssd_inputs(B, T, nh, hd, N, seed=0):
     return dict(x=x, K=K, Q=Q, dt=dt, trap=trap, adt=adt, Dh=np.ones(nh, f), A=A)
 
 
+def m3_group_inputs(B, T, nh, ng, N, n_angles, dt, seed=0):
+    """Group-level inputs of the Mamba-3 K / Q generation: Bn, Cn [B,T,ng,N] ~ N(0,1)
+    * N^-1/4 (what BCNorm leaves, scaled like K and Q above), per-head biases ~ 0.1 N(0,1),
+    angle_vel = tanh(N(0,1)) * pi [B,T,n_angles], a starting angle in [0, 2 pi)."""
+    rng = np.random.default_rng(seed + 7919)
+    f = np.float32
+    sc = f(N) ** f(-0.25)
+    Bn = rng.standard_normal((B, T, ng, N), dtype=f) * sc
+    Cn = rng.standard_normal((B, T, ng, N), dtype=f) * sc
+    b_bias = (0.1 * rng.standard_normal((nh, N), dtype=f) * sc).astype(f)
+    c_bias = (0.1 * rng.standard_normal((nh, N), dtype=f) * sc).astype(f)
+    vel = (np.tanh(rng.standard_normal((B, T, max(n_angles, 1)), dtype=f)) * f(np.pi)).astype(f)[:, :, :n_angles]
+    ang0 = rng.uniform(0.0, 2 * np.pi, size=(B, nh, max(n_angles, 1))).astype(f)[:, :, :n_angles]
+    return dict(Bn=Bn, Cn=Cn, b_bias=b_bias, c_bias=c_bias, angle_vel=np.ascontiguousarray(vel),
+                angle_state=np.ascontiguousarray(ang0))
+
+
+def m3_fused_kq_algorithmic_bytes(B, T, nh, ng, hd, N, n_angles, esize):
+    """x and y, the group-level Bn and Cn once each, angle_vel, dt/trap/adt f32, biases,
+    final state out."""
+    return (2 * esize * B * T * nh * hd + 2 * esize * B * T * ng * N + 4 * B * T * n_angles
+            + 3 * 4 * B * T * nh + 2 * 4 * nh * N + 4 * B * nh * hd * N)
+
+
 def m3_fwd_algorithmic_bytes(B, T, nh, hd, N, esize):
     """x and y, K and Q once each, dt/trap/adt f32, final state out."""
     return (2 * esize * B * T * nh * hd + 2 * esize * B * T * nh * N + 3 * 4 * B * T * nh

@@ -380,6 +380,40 @@ def m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy):
 
 # -- the rows around the scan: residual + RMSNorm, loss, optimiser (numpy) -----------
 
+def m3_kq_from_groups(Bn, Cn, b_bias, c_bias, angle_vel, dt, angle_state=None):
+    """Per-head K and Q of the Mamba-3 SISO layer from the group-level rows, restating
+    src/mamba3_siso/cpu/forward.rs:336-375 (bias add :341-347, angle accumulation in f64
+    modulo 2 pi rounded to f32 per step :352-359, rotation of the pairs (2a, 2a+1) :360-372;
+    the GPU kernels bc_bias_add / m3_angle_dt_fwd_seq / rope_fwd of kernels/mamba3_ops.cu
+    compute the same).  Bn, Cn [B,T,ng,N]; b_bias, c_bias [nh,N]; angle_vel [B,T,n_angles]
+    = tanh(angles_raw) * pi; dt [B,T,nh]; angle_state [B,nh,n_angles] (None = zeros).
+    Returns K, Q [B,T,nh,N] f32 and the angle after the window [B,nh,n_angles] f32."""
+    f = np.float32
+    Bn, Cn = np.asarray(Bn, f), np.asarray(Cn, f)
+    Bsz, T, ng, N = Bn.shape
+    nh = b_bias.shape[0]
+    na = angle_vel.shape[2] if angle_vel is not None else 0
+    grp = np.arange(nh) // (nh // ng)
+    K = (Bn[:, :, grp, :] + np.asarray(b_bias, f)[None, None]).astype(f)
+    Q = (Cn[:, :, grp, :] + np.asarray(c_bias, f)[None, None]).astype(f)
+    ang = np.zeros((Bsz, nh, max(na, 1)), f) if angle_state is None else np.array(angle_state, f)
+    if na:
+        two_pi = 2.0 * np.pi
+        vel, dtf = np.asarray(angle_vel, f), np.asarray(dt, f)
+        for t in range(T):
+            delta = (vel[:, t, None, :] * dtf[:, t, :, None]).astype(f)      # f32 product, forward.rs:354
+            acc = ang[:, :, :na].astype(np.float64) + delta.astype(np.float64)
+            acc -= two_pi * np.floor(acc / two_pi)
+            ang[:, :, :na] = acc.astype(f)
+            a32 = ang[:, :, :na]
+            sn, cs = np.sin(a32).astype(f), np.cos(a32).astype(f)
+            for X in (K, Q):
+                x0, x1 = X[:, t, :, 0:2 * na:2].copy(), X[:, t, :, 1:2 * na:2].copy()
+                X[:, t, :, 0:2 * na:2] = cs * x0 - sn * x1
+                X[:, t, :, 1:2 * na:2] = sn * x0 + cs * x1
+    return K, Q, ang[:, :, :na].copy()
+
+
 def residual_rmsnorm_fwd(residual, branch, scale, eps=1e-5):
     """residual_add_f32_{dt} (kernels/elementwise.cu:367-377) followed by
     rmsnorm_forward_f32in_{dt} (kernels/norms.cu:126-168), in f32: returns the new

@@ -231,3 +231,37 @@ def test_det_rand_stream():
         exp.append((s & 0xFFFF) / 65536.0 - 0.5)
     np.testing.assert_allclose(v, exp, rtol=0, atol=1e-7)
     assert np.all(v >= -0.5) and np.all(v < 0.5)
+
+
+# --- Mamba-3 per-head K / Q from the group-level rows (bias + RoPE) ---
+def test_m3_kq_generation_properties():
+    from mamba_rs_b200 import synth
+    B, T, nh, ng, N, na = 2, 37, 4, 2, 16, 4
+    i = synth.m3_ssd_inputs(B, T, nh, 8, N, seed=5)
+    g = synth.m3_group_inputs(B, T, nh, ng, N, na, i["dt"], seed=5)
+    K, Q, ang = oracle.m3_kq_from_groups(g["Bn"], g["Cn"], g["b_bias"], g["c_bias"], g["angle_vel"], i["dt"],
+                                         g["angle_state"])
+    grp = np.arange(nh) // (nh // ng)
+    Kb = g["Bn"][:, :, grp, :] + g["b_bias"][None, None]
+    # columns past 2 * n_angles pass through with the bias only (kernels/mamba3_ops.cu:607-611)
+    np.testing.assert_array_equal(K[..., 2 * na:], Kb[..., 2 * na:])
+    # a rotation keeps the length of every pair
+    n2 = lambda X: X[..., 0:2 * na:2] ** 2 + X[..., 1:2 * na:2] ** 2
+    np.testing.assert_allclose(n2(K), n2(Kb), rtol=2e-5, atol=1e-7)
+    # the angle is the running sum of angle_vel * dt, modulo 2 pi
+    want = g["angle_state"].astype(np.float64) + np.einsum("bta,bth->bha", g["angle_vel"].astype(np.float64),
+                                                           i["dt"].astype(np.float64))
+    d = np.abs(ang - np.mod(want, 2 * np.pi))
+    assert np.minimum(d, 2 * np.pi - d).max() < 1e-4
+    # a window split in two, carrying the angle, equals the whole window bit for bit
+    h = 20
+    K1, Q1, a1 = oracle.m3_kq_from_groups(g["Bn"][:, :h], g["Cn"][:, :h], g["b_bias"], g["c_bias"],
+                                          g["angle_vel"][:, :h], i["dt"][:, :h], g["angle_state"])
+    K2, Q2, a2 = oracle.m3_kq_from_groups(g["Bn"][:, h:], g["Cn"][:, h:], g["b_bias"], g["c_bias"],
+                                          g["angle_vel"][:, h:], i["dt"][:, h:], a1)
+    np.testing.assert_array_equal(np.concatenate([K1, K2], 1), K)
+    np.testing.assert_array_equal(np.concatenate([Q1, Q2], 1), Q)
+    np.testing.assert_array_equal(a2, ang)
+    # no angles: bias add only
+    K0, Q0, _ = oracle.m3_kq_from_groups(g["Bn"], g["Cn"], g["b_bias"], g["c_bias"], None, i["dt"])
+    np.testing.assert_array_equal(K0, Kb.astype(np.float32))
