@@ -131,10 +131,8 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // state for the next chunk's Y2; then f32 vectors, barriers.
 constexpr uint32_t kQ = 0, kM = 0, kK = 32768, kV = 65536, kVw = 81920, kS = 81920;
 constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128]
-// K / Q generation: per-warp angle totals [4][64], entering angle f32 [64] and f64 [64],
-// this head's B / C biases [2][128]
-constexpr uint32_t kWtot = kVec + 5 * 128 * 4, kBase = kWtot + 4 * 64 * 4, kCarry = kBase + 64 * 4,
-                   kBias = kCarry + 64 * 8;
+// K / Q generation: the angle entering the chunk, f64 [64]; this head's B / C biases [2][128]
+constexpr uint32_t kCarry = kVec + 5 * 128 * 4, kBias = kCarry + 64 * 8;
 constexpr uint32_t kBar = kBias + 2 * 128 * 4, kTmemSlot = kBar + 16;
 constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
@@ -144,9 +142,8 @@ constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
 //   K[t,h,:] = rope(Bn[t,g,:] + b_bias[h,:], angle[t,h,:]),  Q likewise from Cn / c_bias,
 //   angle[t,h,a] = (angle_in[h,a] + sum_{s<=t} angle_vel[s,a] * dt[s,h]) mod 2 pi
 // (src/mamba3_siso/cpu/forward.rs:336-375; kernels/mamba3_ops.cu:279-310, :400-440,
-// :575-640).  Thread (row, half) owns the 16-byte pieces j = half, half + 2, ... of its
-// row; the in-chunk sums run as shuffle scans over the rows, the angle entering a chunk
-// is carried in f64.
+// :575-640).  The in-chunk sums run in f32 (shuffle scans over the rows), the angle
+// entering a chunk is carried in f64.
 template <typename Th, bool GEN>
 __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -171,8 +168,6 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         fence_barrier_init();
     }
     float* dtv = vec + 512;
-    float* wtot = reinterpret_cast<float*>(smem + kWtot);
-    float* basef = reinterpret_cast<float*>(smem + kBase);
     double* carry = reinterpret_cast<double*>(smem + kCarry);
     float* bias_sm = reinterpret_cast<float*>(smem + kBias);
     if (GEN) {
@@ -181,7 +176,6 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             const float v = (a < p.n_angles && p.angle_state)
                                 ? p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + a] : 0.0f;
             carry[a] = static_cast<double>(v);
-            basef[a] = v;
         }
         const float* bsrc = half ? p.c_bias : p.b_bias;
         bias_sm[half * 128 + tid] = tid < nsv ? bsrc[static_cast<long long>(h) * nsv + tid] : 0.0f;
@@ -270,105 +264,141 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     };
 
 
-    // K and Q tiles of chunk c from the group-level rows (GEN only).
-    auto gen_qk = [&](int c) {
+    // K and Q tiles of chunk c from the group-level rows (GEN only).  Thread (lane, warp w)
+    // owns the 16-byte pieces j = w and w + 8 of the rows lane, lane + 32, lane + 64,
+    // lane + 96: it copies exactly those pieces of Bn / Cn into the K / Q tiles
+    // (gen_issue, asynchronous) and later rewrites them in place (gen_apply), so no
+    // block-wide barrier sits between the two.  The angle of (row, a) is the angle
+    // entering the chunk (f64, shared memory) plus an inclusive sum over the rows: a
+    // warp shuffle scan inside each block of 32 rows and a running prefix over the four
+    // blocks, which the same thread owns.
+    auto gen_issue = [&](int c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
-        const bool rok = tid < nv;
-        const long long bt = static_cast<long long>(b) * T + t0 + (rok ? tid : 0);
-        const int na = p.n_angles;
-        constexpr double kTwoPi64 = 6.283185307179586;
-        // the angle entering this chunk: previous entering angle + the previous chunk's sums
-        if (c > 0 && threadIdx.x < na) {
-            const int a = threadIdx.x;
-            double sacc = carry[a] + (static_cast<double>(wtot[a]) + static_cast<double>(wtot[64 + a]) +
-                                      static_cast<double>(wtot[128 + a]) + static_cast<double>(wtot[192 + a]));
-            sacc -= kTwoPi64 * floor(sacc / kTwoPi64);
-            carry[a] = sacc;
-            basef[a] = static_cast<float>(sacc);
-        }
-        // angle increments of this row, then the inclusive sums over the rows of the warp
-        const float dtr = rok ? dtv[tid] : 0.0f;
-        float cum[8][4];
+        const int grp = h / (nh / p.ng);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int j = 2 * k + half;
-            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (4 * j < na && rok) v = __ldg(reinterpret_cast<const float4*>(p.angle_vel + bt * na + 4 * j));
-            cum[k][0] = v.x * dtr; cum[k][1] = v.y * dtr; cum[k][2] = v.z * dtr; cum[k][3] = v.w * dtr;
-        }
+        for (int which = 0; which < 2; ++which) {
+            const Th* base = static_cast<const Th*>(which ? p.Cn : p.Bn) +
+                             ((static_cast<long long>(b) * T + t0) * p.ng + grp) * nsv;
+            const uint32_t tile = which ? kQ : kK;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            if (4 * (2 * k + half) < na) {
+            for (int i = 0; i < 4; ++i) {
+                const int row = lane + 32 * i;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float v = cum[k][e];
-#pragma unroll
-                    for (int m = 1; m < 32; m <<= 1) {
-                        const float o = __shfl_up_sync(0xffffffffu, v, m);
-                        if (lane >= m) v += o;
-                    }
-                    cum[k][e] = v;
+                for (int q = 0; q < 2; ++q) {
+                    const int j = wfull + 8 * q;
+                    const bool ok = row < nv && 8 * j < nsv;
+                    cp_async16(smem + tile + chunk_off(row, j, NS),
+                               base + static_cast<long long>(min(row, nv - 1)) * p.ng * nsv + (ok ? 8 * j : 0), ok);
                 }
             }
         }
-        __syncthreads();  // the previous totals have been folded into the entering angle
-        if (lane == 31) {
+    };
+    auto gen_apply = [&](int c) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const int na = p.n_angles;
+        constexpr double kTwoPi64 = 6.283185307179586, kInvTwoPi64 = 0.15915494309189535;
+        float4 vel[4][2];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (4 * (2 * k + half) < na) {
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) wtot[warp * 64 + 4 * (2 * k + half) + e] = cum[k][e];
-                }
-        }
-        __syncthreads();
-        const Th* Bg = static_cast<const Th*>(p.Bn);
-        const Th* Cg = static_cast<const Th*>(p.Cn);
-        const int grp = h / (nh / p.ng);
-        const long long rowoff = (bt * p.ng + grp) * nsv;
+            for (int q = 0; q < 2; ++q) {
+                const int j = wfull + 8 * q, row = lane + 32 * i;
+                vel[i][q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (4 * j < na && row < nv)
+                    vel[i][q] = __ldg(reinterpret_cast<const float4*>(
+                        p.angle_vel + (static_cast<long long>(b) * T + t0 + row) * na + 4 * j));
+            }
+        float base[2][4], pre[2][4];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int j = 2 * k + half;
-            uint4 ko = make_uint4(0, 0, 0, 0), qo = ko;
-            if (8 * j < nsv && rok) {
-                const uint4 braw = __ldg(reinterpret_cast<const uint4*>(Bg + rowoff + 8 * j));
-                const uint4 craw = __ldg(reinterpret_cast<const uint4*>(Cg + rowoff + 8 * j));
-                const uint32_t bw[4] = {braw.x, braw.y, braw.z, braw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w};
-                const float4 bb0 = *reinterpret_cast<const float4*>(bias_sm + 8 * j);
-                const float4 bb1 = *reinterpret_cast<const float4*>(bias_sm + 8 * j + 4);
-                const float4 cb0 = *reinterpret_cast<const float4*>(bias_sm + 128 + 8 * j);
-                const float4 cb1 = *reinterpret_cast<const float4*>(bias_sm + 128 + 8 * j + 4);
-                const float bbv[8] = {bb0.x, bb0.y, bb0.z, bb0.w, bb1.x, bb1.y, bb1.z, bb1.w};
-                const float cbv[8] = {cb0.x, cb0.y, cb0.z, cb0.w, cb1.x, cb1.y, cb1.z, cb1.w};
-                uint32_t kw[4], qw[4];
-                const bool rot = 4 * j < na;
+        for (int q = 0; q < 2; ++q)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 bf = unpack2<Th>(bw[e]), cf = unpack2<Th>(cw[e]);
-                    float k0 = bf.x + bbv[2 * e], k1 = bf.y + bbv[2 * e + 1];
-                    float q0 = cf.x + cbv[2 * e], q1 = cf.y + cbv[2 * e + 1];
-                    if (rot) {
-                        const int a = 4 * j + e;
-                        float ang = basef[a] + cum[k][e];
-                        for (int w = 0; w < warp; ++w) ang += wtot[w * 64 + a];
+            for (int e = 0; e < 4; ++e) {
+                const int a = 4 * (wfull + 8 * q) + e;
+                base[q][e] = a < na ? static_cast<float>(carry[a]) : 0.0f;
+                pre[q][e] = 0.0f;
+            }
+        asm volatile("cp.async.wait_all;" ::: "memory");  // this thread's own pieces have landed
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = lane + 32 * i;
+            const bool rok = row < nv;
+            const float dtr = rok ? dtv[row] : 0.0f;
+            float sn[2][4], cs[2][4];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (4 * (wfull + 8 * q) < na) {
+                    const float vv[4] = {vel[i][q].x, vel[i][q].y, vel[i][q].z, vel[i][q].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float v = vv[e] * dtr;
+#pragma unroll
+                        for (int m = 1; m < 32; m <<= 1) {
+                            const float o = __shfl_up_sync(0xffffffffu, v, m);
+                            if (lane >= m) v += o;
+                        }
+                        float ang = base[q][e] + pre[q][e] + v;
+                        pre[q][e] += __shfl_sync(0xffffffffu, v, 31);
                         // to [-pi, pi] before the fast sine / cosine
                         const float turns = rintf(ang * 0.15915494309189535f);
                         ang = fmaf(turns, -6.2831854820251465f, ang);
                         ang = fmaf(turns, 1.7484555e-7f, ang);
-                        float sn, cs;
-                        __sincosf(ang, &sn, &cs);
-                        const float rk0 = cs * k0 - sn * k1, rk1 = sn * k0 + cs * k1;
-                        const float rq0 = cs * q0 - sn * q1, rq1 = sn * q0 + cs * q1;
-                        k0 = rk0; k1 = rk1; q0 = rq0; q1 = rq1;
+                        __sincosf(ang, &sn[q][e], &cs[q][e]);
                     }
-                    kw[e] = pack2<Th>(k0, k1);
-                    qw[e] = pack2<Th>(q0, q1);
                 }
-                ko = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-                qo = make_uint4(qw[0], qw[1], qw[2], qw[3]);
             }
-            *reinterpret_cast<uint4*>(smem + kK + chunk_off(tid, j, NS)) = ko;
-            *reinterpret_cast<uint4*>(smem + kQ + chunk_off(tid, j, NS)) = qo;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int j = wfull + 8 * q;
+                if (8 * j < nsv && rok) {
+                    const bool rot = 4 * j < na;
+#pragma unroll
+                    for (int which = 0; which < 2; ++which) {
+                        uint4* pp = reinterpret_cast<uint4*>(smem + (which ? kQ : kK) + chunk_off(row, j, NS));
+                        const uint4 raw = *pp;
+                        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                        const float4 b0 = *reinterpret_cast<const float4*>(bias_sm + which * 128 + 8 * j);
+                        const float4 b1 = *reinterpret_cast<const float4*>(bias_sm + which * 128 + 8 * j + 4);
+                        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                        uint32_t ow[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = unpack2<Th>(rw[e]);
+                            float v0 = f.x + bv[2 * e], v1 = f.y + bv[2 * e + 1];
+                            if (rot) {
+                                const float r0 = cs[q][e] * v0 - sn[q][e] * v1, r1 = sn[q][e] * v0 + cs[q][e] * v1;
+                                v0 = r0; v1 = r1;
+                            }
+                            ow[e] = pack2<Th>(v0, v1);
+                        }
+                        *pp = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
+                }
+            }
         }
+        // fold this chunk's sums into the entering angle of the next one
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int a = 4 * (wfull + 8 * q) + e;
+                if (a < na) {
+                    double sacc = carry[a] + static_cast<double>(pre[q][e]);
+                    sacc -= kTwoPi64 * floor(sacc * kInvTwoPi64);
+                    __syncwarp();
+                    if (lane == 0) carry[a] = sacc;
+                }
+            }
+    };
+
+    auto issue_tiles = [&](int c) {
+        if (GEN) {
+            gen_issue(c);
+        } else {
+            issue_qk(Qg, kQ, c);
+            issue_qk(Kg, kK, c);
+        }
+        issue_v(kV, c);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     for (int c = 0; c < nchunks; ++c) {
@@ -380,14 +410,10 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         const float* gam = dA + 256;
         const uint32_t tK = kK, tV = kV;
         // ---- 1. this chunk's Q, K, V tiles (asynchronous copies) and per-row scalars ----
-        if (!GEN) {
-            issue_qk(Qg, kQ, c);
-            issue_qk(Kg, kK, c);
-        }
-        issue_v(kV, c);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        // (issuing chunk c + 1 during the epilogue of chunk c was measured: 5 % slower)
+        issue_tiles(c);
         scalars(c, 0);
-        if (GEN) gen_qk(c);
+        if (GEN) gen_apply(c);
         asm volatile("cp.async.wait_all;" ::: "memory");
         fence_proxy_async();
         fence_before();
@@ -545,14 +571,9 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             if (p.k_state && half == 0 && tid < nsv)
                 p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] =
                     to_f(*reinterpret_cast<const Th*>(smem + kK + chunk_off(lr, tid >> 3, NS) + (tid & 7) * 2));
-            if (p.angle_state && threadIdx.x < p.n_angles) {
-                const int a = threadIdx.x;
-                constexpr double kTwoPi64 = 6.283185307179586;
-                double sacc = carry[a] + (static_cast<double>(wtot[a]) + static_cast<double>(wtot[64 + a]) +
-                                          static_cast<double>(wtot[128 + a]) + static_cast<double>(wtot[192 + a]));
-                sacc -= kTwoPi64 * floor(sacc / kTwoPi64);
-                p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + a] = static_cast<float>(sacc);
-            }
+            if (p.angle_state && threadIdx.x < p.n_angles)
+                p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + threadIdx.x] =
+                    static_cast<float>(carry[threadIdx.x]);
         } else if (p.k_state && half == 0 && tid < nsv)
             p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] = to_f(Kg[(last * nh + h) * nsv + tid]);
         if (p.v_state && half == 0 && tid < hdv)
