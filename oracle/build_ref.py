@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 ENV_REF = "MAMBA_RS_REFERENCE"
-FILES = ["mamba_ssm_parallel.cu", "mamba_ssm.cu", "conv1d.cu", "mamba3_chunked.cu", "mamba3_ssd.cu"]
+FILES = ["mamba_ssm_parallel.cu", "mamba_ssm.cu", "conv1d.cu", "mamba3_chunked.cu", "mamba3_ssd.cu", "mamba3_ops.cu"]
 
 
 def build_ref(ref_root: str = "", verbose: bool = False) -> bool:

@@ -15,7 +15,7 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _REF = os.path.join(_HERE, "_ref")
-MODULES = ("mamba_ssm_parallel", "mamba_ssm", "conv1d", "mamba3_ssd", "mamba3_chunked")
+MODULES = ("mamba_ssm_parallel", "mamba_ssm", "conv1d", "mamba3_ssd", "mamba3_chunked", "mamba3_ops")
 
 
 def available() -> bool:
@@ -255,6 +255,30 @@ class RefKernels:
                      [y, x, Q, Ks, qk, dacs, states, Dh, Bsz, T, nh, hd, N, CS])
         return dict(y=y, final_state=final, K_scaled=Ks, qk_dot=qk, scale=scale, gamma=gam, dA_cumsum=dacs,
                     chunk_states=states)
+
+    def m3_kq_from_groups(self, Bn, Cn, b_bias, c_bias, angles_raw, dtv, angle_state):
+        """The reference's per-head K / Q chain in f32: bc_bias_add (x2) -> m3_angle_dt_fwd_seq ->
+        rope_fwd (kernels/mamba3_ops.cu:279-310, :400-440, :575-640; launch sites
+        src/mamba3_siso/gpu/forward.rs:170-255).  Bn, Cn [B,T,ng,N], biases [nh,N], angles_raw
+        [B,T,n_angles], dtv [B,T,nh], angle_state [B,nh,n_angles] (updated in place).
+        Returns K, Q [B,T,nh,N] and the per-step angles [B,T,nh,n_angles]."""
+        import torch
+        Bsz, T, ng, N = Bn.shape
+        nh = b_bias.shape[0]
+        na = angles_raw.shape[2]
+        f32 = dict(dtype=torch.float32, device=Bn.device)
+        rows = Bsz * T
+        Kb, Qb = torch.empty(Bsz, T, nh, N, **f32), torch.empty(Bsz, T, nh, N, **f32)
+        fn = self._func("mamba3_ops", "bc_bias_add")
+        self._launch(fn, self._grid_1d(rows * nh * N), 256, 0, [Kb, Bn, b_bias, rows, nh, ng, N])
+        self._launch(fn, self._grid_1d(rows * nh * N), 256, 0, [Qb, Cn, c_bias, rows, nh, ng, N])
+        cum = torch.empty(Bsz, T, nh, na, **f32)
+        self._launch(self._func("mamba3_ops", "m3_angle_dt_fwd_seq"), (Bsz, (nh * na + 255) // 256, 1), 256, 0,
+                     [cum, angle_state, angles_raw, dtv, Bsz, T, nh, na])
+        K, Q = torch.empty_like(Kb), torch.empty_like(Qb)
+        self._launch(self._func("mamba3_ops", "rope_fwd"), self._grid_1d(rows * nh * N), 256, 0,
+                     [K, Q, Kb, Qb, cum, rows, nh, N, na])
+        return K, Q, cum
 
     def m3_dqkv(self, dt, fw, x, Q, Dh, dy, CS=64):
         """m3_extract_da_cs_sum + m3_dqkv[_{bf16,f16}] (kernels/mamba3_chunked.cu:439-794,

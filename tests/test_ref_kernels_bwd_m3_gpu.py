@@ -297,3 +297,41 @@ def test_reference_m3_chunked_forward_and_backward(cuda_dev, rk, case, dt):
     for k in ("dx", "dK", "dQ", "d_adt", "d_dt", "d_trap_raw", "dD"):
         assert rel_err(ref_b[k], orc_b[k]) <= tol, ("reference vs oracle", k)
         assert rel_err(lib_b[k], ref_b[k]) <= tol, ("library vs reference", k)
+
+
+# --- Mamba-3 per-head K / Q: reference chain bc_bias_add -> m3_angle_dt_fwd_seq -> rope_fwd ---
+@pytest.mark.parametrize("shape", [(2, 300, 4, 1, 128, 32), (1, 129, 4, 2, 64, 32), (2, 70, 2, 1, 32, 8)])
+def test_reference_m3_kq_chain_agrees_with_oracle_and_fused_kernel(cuda_dev, rk, shape):
+    """reference kernels ~ oracle.m3_kq_from_groups (f32, 1e-4), and the tensor-core kernel
+    that builds K / Q itself ~ the scan oracle fed the reference kernels' K / Q (bf16, 2e-2)."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    from mamba_rs_b200 import synth
+    B, T, nh, ng, N, na = shape
+    hd = 32
+    i = synth.m3_ssd_inputs(B, T, nh, hd, N, seed=21)
+    g = synth.m3_group_inputs(B, T, nh, ng, N, na, i["dt"], seed=21)
+    raw = np.random.default_rng(5).standard_normal((B, T, na)).astype(np.float32)
+    vel = (np.tanh(raw) * np.float32(np.pi)).astype(np.float32)
+    bf = lambda a: synth.round_to(a, "bf16")
+    Bn, Cn, x = bf(g["Bn"]), bf(g["Cn"]), bf(i["x"])
+    t = lambda a, d=None: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_dev).to(d or torch.float32)
+    ang_ref = t(g["angle_state"])
+    Kr, Qr, cum = rk.m3_kq_from_groups(t(Bn), t(Cn), t(g["b_bias"]), t(g["c_bias"]), t(raw), t(i["dt"]), ang_ref)
+    torch.cuda.synchronize()
+    Ko, Qo, ang_o = oracle.m3_kq_from_groups(Bn, Cn, g["b_bias"], g["c_bias"], vel, i["dt"], g["angle_state"])
+    assert rel_err(Kr.cpu().numpy(), Ko) <= 1e-4
+    assert rel_err(Qr.cpu().numpy(), Qo) <= 1e-4
+    d = np.abs(ang_ref.cpu().numpy() - ang_o)
+    assert np.minimum(d, 2 * np.pi - d).max() <= 1e-4
+
+    ref = oracle.m3_ssd_fwd(x, bf(Kr.cpu().numpy()), bf(Qr.cpu().numpy()), i["dt"], i["trap"], i["adt"], i["Dh"])
+    tb = torch.bfloat16
+    ang = t(g["angle_state"])
+    y = mb.ops.m3_ssd_fwd_fused_kq(t(x, tb), t(Bn, tb), t(Cn, tb), t(g["b_bias"]), t(g["c_bias"]), t(vel),
+                                   t(i["dt"]), t(i["trap"]), t(i["adt"]), t(i["Dh"]), angle_state=ang)
+    torch.cuda.synchronize()
+    assert rel_err(y.float().cpu().numpy(), ref["y"]) <= TOL["bf16"]
+    d = np.abs(ang.cpu().numpy() - ang_ref.cpu().numpy())
+    assert np.minimum(d, 2 * np.pi - d).max() <= 1e-3
