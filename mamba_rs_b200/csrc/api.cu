@@ -39,6 +39,24 @@ bool make_tmap_3d(Ctx* c, CUtensorMap* map, int dtype, const void* base, long lo
     return r == CUDA_SUCCESS;
 }
 
+bool make_tmap_head_tile(Ctx* c, CUtensorMap* map, int dtype, const void* base, int cols, int heads, int T,
+                         int B) {
+    if (!c->encode_tiled || !base || dtype == MAMBA_B200_F32) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || cols % 8 != 0 || cols < 8 || heads < 1) return false;
+    const cuuint64_t rs = static_cast<cuuint64_t>(heads) * cols * 2;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(heads),
+                          static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(cols) * 2, rs, rs * static_cast<cuuint64_t>(T)};
+    if (strides[2] >= (1ull << 40)) return false;
+    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(c->encode_tiled)(
+        map, dtype == MAMBA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 int m1_fwd_configure(Ctx* c);   // m1_fwd.cu: raises dynamic shared-memory limits
 int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
 int m3_configure(Ctx* c);       // m3_ssd.cu

@@ -41,6 +41,13 @@ inline bool dtype_ok(int dtype) {
 bool make_tmap_3d(Ctx* c, CUtensorMap* map, int dtype, const void* base, long long ld, int cols,
                   int T, int B, int box_cols, int box_rows);
 
+// Describes a 16-bit [B, T, heads, cols] tensor (contiguous) as a 4-D TMA tensor with a box
+// of 64 columns x 1 head x 128 rows and 128-byte swizzle: one copy lands a [128 x 64]
+// sub-tile of the Mamba-3 tensor-core kernels; columns past `cols` and rows past T read as
+// zeros.
+bool make_tmap_head_tile(Ctx* c, CUtensorMap* map, int dtype, const void* base, int cols, int heads, int T,
+                         int B);
+
 #define MB200_CUDA_CHECK(ctx, expr)                                                          \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \

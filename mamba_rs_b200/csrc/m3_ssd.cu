@@ -22,6 +22,8 @@
 namespace mb200 {
 
 struct M3Params {
+    // tensor-core kernel: Q (or Cn), K (or Bn) and x as [128 x 64] swizzled sub-tile maps
+    CUtensorMap tm_q, tm_k, tm_v, tm_y;
     const void *x, *K, *Q;
     const float *dt, *trap, *adt, *Dh;
     void* y;
@@ -122,21 +124,25 @@ __global__ void m3_ssd_seq_kernel(const M3Params p) {
 namespace tc {
 
 constexpr int CS = 128, HD = 64, NS = 128;
-// Shared-memory operand tiles: 8-row x 16-byte core matrices (no swizzle).  A
-// tile of R rows x C 16-bit columns keeps core (r/8, c/8) at
-// (r/8)*(C/8)*128 + (c/8)*128 bytes, row r%8 at +16*(r%8).
-// Tiles, sized so that TWO CTAs share an SM (their load, MMA and epilogue
-// phases overlap each other): Q, reused for M once G is done; K; V; one tile
-// that holds w o V for the state update and then the 16-bit copy of the new
-// state for the next chunk's Y2; then f32 vectors, barriers.
-constexpr uint32_t kQ = 0, kM = 0, kK = 32768, kV = 65536, kVw = 81920, kS = 81920;
-constexpr uint32_t kVec = 98304;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128]
+// Shared-memory operand tiles are 128-byte-swizzled [rows x 64] sub-tiles (m3_tc.cuh); TMA
+// lands Q, K and V in that form.  One CTA per SM.  Q, K and V are double-buffered: the
+// copies of chunk c + 1 are issued (one thread, five boxes) before chunk c is touched, so a
+// whole chunk of work hides their latency -- with single buffers, two CTAs per SM and
+// 16-byte asynchronous copies, 7.6 of the 11.5 us a chunk took were spent waiting for its
+// tiles.  M has its own tile; one more tile holds w o V for the state update and then the
+// 16-bit copy of the new state for the next chunk's Y2; then f32 vectors, barriers.
+constexpr uint32_t kQ0 = 0, kK0 = 65536, kV0 = 131072, kQKStride = 32768, kVStride = 16384;
+constexpr uint32_t kM = 163840, kVw = 196608, kS = 196608;
+constexpr uint32_t kVec = 212992;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128]
 // K / Q generation: the angle entering the chunk, f64 [64]; this head's B / C biases [2][128]
 constexpr uint32_t kCarry = kVec + 5 * 128 * 4, kBias = kCarry + 64 * 8;
-constexpr uint32_t kBar = kBias + 2 * 128 * 4, kTmemSlot = kBar + 16;
+// per-row adt, dt, trap of a chunk (dt and trap with the row after it), two buffers,
+// filled by 4-byte asynchronous copies
+constexpr uint32_t kStage = kBias + 2 * 128 * 4, kStageBuf = 3 * 132 * 4;
+constexpr uint32_t kBar = kStage + 2 * kStageBuf, kTmemSlot = kBar + 32;
 constexpr uint32_t kSmem = kTmemSlot + 16;
-// TMEM columns (256 per CTA): G, whose first 64 columns later take Y1; Y2; S^T.
-constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
+// TMEM columns: G; Y1; Y2; S^T.
+constexpr uint32_t cG = 0, cY1 = 256, cY2 = 320, cS = 384, kTmemCols = 512;
 
 // GEN: build the K and Q tiles of a chunk in the kernel instead of reading them:
 //   K[t,h,:] = rope(Bn[t,g,:] + b_bias[h,:], angle[t,h,:]),  Q likewise from Cn / c_bias,
@@ -145,7 +151,7 @@ constexpr uint32_t cG = 0, cY1 = 0, cY2 = 128, cS = 192, kTmemCols = 256;
 // :575-640).  The in-chunk sums run in f32 (shuffle scans over the rows), the angle
 // entering a chunk is carried in f64.
 template <typename Th, bool GEN>
-__global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p) {
+__global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_constant__ M3Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // two threads per step: thread (row, half) owns row `row` of the chunk (TMEM lane
     // `row`) and half of that row's columns in every elementwise stage
@@ -162,9 +168,12 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + kTmemSlot);
     const uint32_t sbase = smem_u32(smem);
 
+    uint64_t* full = bars + 2;  // tiles of buffer 0 / 1 have landed (TMA)
     if (threadIdx.x == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
         fence_barrier_init();
     }
     float* dtv = vec + 512;
@@ -194,56 +203,40 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
 
     const Th* xg = static_cast<const Th*>(p.x);
     const Th* Kg = static_cast<const Th*>(p.K);
-    const Th* Qg = static_cast<const Th*>(p.Q);
-    Th* yg = static_cast<Th*>(p.y);
     const float Dv = p.Dh[h];
     const int nchunks = (T + CS - 1) / CS;
     bool ok = true;
 
-    // Cooperative tile loads: one warp instruction moves 8 rows x 64 bytes (whole
-    // 32-byte sectors in global memory, 512 contiguous bytes of the tile).
-    const int r8 = lane & 7, jc = lane >> 3;
-    auto issue_qk = [&](const Th* src, uint32_t tile, int c) {
-        const int t0 = c * CS, nv = min(CS, T - t0);
-        const Th* base = src + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv;
-        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int task = i * 8 + wfull, rg = task >> 2, jg = task & 3, row = rg * 8 + r8;
-            const int col = 8 * jc + 32 * jg;
-            const bool ok = row < nv && col < nsv;
-            cp_async16(smem + dst0 + rg * 2048 + jg * 512,
-                       base + static_cast<long long>(min(row, nv - 1)) * nh * nsv + (ok ? col : 0), ok);
-        }
-    };
-    auto issue_v = [&](uint32_t tile, int c) {
-        const int t0 = c * CS, nv = min(CS, T - t0);
-        const Th* base = xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv;
-        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int task = i * 8 + wfull, rg = task >> 1, jg = task & 1, row = rg * 8 + r8;
-            const int col = 8 * jc + 32 * jg;
-            const bool ok = row < nv && col < hdv;
-            cp_async16(smem + dst0 + rg * 1024 + jg * 512,
-                       base + static_cast<long long>(min(row, nv - 1)) * nh * hdv + (ok ? col : 0), ok);
-        }
-    };
     // Per-row scalars of chunk c into stage `st`: inclusive cumsum of adt, scale, gamma.
+    // Per-row scalars travel a chunk ahead as 4-byte asynchronous copies into shared memory:
+    // with nheads > 1 they are 128-byte-strided words, and as register loads they were
+    // drained by every proxy fence of the chunk (0.18 ms of 0.45 ms at 32 heads).
+    auto stage_scalars = [&](int c) {
+        if (c < nchunks && threadIdx.x <= CS) {
+            float* st = reinterpret_cast<float*>(smem + kStage + (c & 1) * kStageBuf);
+            const int r = threadIdx.x, t = c * CS + r;
+            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+            if (t < T) {
+                if (r < CS) cp_async4(st + r, p.adt + th);
+                cp_async4(st + 132 + r, p.dt + th);
+                cp_async4(st + 264 + r, p.trap + th);
+            } else {
+                if (r < CS) st[r] = 0.0f;
+                st[132 + r] = 0.0f;
+                st[264 + r] = 0.0f;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     auto scalars = [&](int c, int st) {
         float* dA = vec + st * 384;
         float* scl = dA + 128;
         float* gam = dA + 256;
-        const int t0 = c * CS, nv = min(CS, T - t0), t = t0 + tid;
-        float a = 0.0f, g = 0.0f, s = 0.0f, dtr = 0.0f;
-        if (tid < nv) {
-            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
-            a = p.adt[th];
-            dtr = p.dt[th];
-            g = dtr * p.trap[th];
-            s = g;
-            if (t + 1 < T) s += p.dt[th + nh] * (1.0f - p.trap[th + nh]);
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // every thread's staged words of this chunk are in shared memory
+        const float* stg = reinterpret_cast<const float*>(smem + kStage + (c & 1) * kStageBuf);
+        const float a = stg[tid], dtr = stg[132 + tid], g = dtr * stg[264 + tid];
+        const float s = g + stg[132 + tid + 1] * (1.0f - stg[264 + tid + 1]);
         float run = a;
 #pragma unroll
         for (int m = 1; m < 32; m <<= 1) {
@@ -264,96 +257,106 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
     };
 
 
-    // K and Q tiles of chunk c from the group-level rows (GEN only).  Thread (lane, warp w)
-    // owns the 16-byte pieces j = w and w + 8 of the rows lane, lane + 32, lane + 64,
-    // lane + 96: it copies exactly those pieces of Bn / Cn into the K / Q tiles
-    // (gen_issue, asynchronous) and later rewrites them in place (gen_apply), so no
-    // block-wide barrier sits between the two.  The angle of (row, a) is the angle
-    // entering the chunk (f64, shared memory) plus an inclusive sum over the rows: a
-    // warp shuffle scan inside each block of 32 rows and a running prefix over the four
-    // blocks, which the same thread owns.
-    auto gen_issue = [&](int c) {
-        const int t0 = c * CS, nv = min(CS, T - t0);
-        const int grp = h / (nh / p.ng);
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-            const Th* base = static_cast<const Th*>(which ? p.Cn : p.Bn) +
-                             ((static_cast<long long>(b) * T + t0) * p.ng + grp) * nsv;
-            const uint32_t tile = which ? kQ : kK;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int row = lane + 32 * i;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int j = wfull + 8 * q;
-                    const bool ok = row < nv && 8 * j < nsv;
-                    cp_async16(smem + tile + chunk_off(row, j, NS),
-                               base + static_cast<long long>(min(row, nv - 1)) * p.ng * nsv + (ok ? 8 * j : 0), ok);
-                }
-            }
-        }
-    };
-    auto gen_apply = [&](int c) {
-        const int t0 = c * CS, nv = min(CS, T - t0);
-        const int na = p.n_angles;
-        constexpr double kTwoPi64 = 6.283185307179586, kInvTwoPi64 = 0.15915494309189535;
-        float4 vel[4][2];
+    // K and Q tiles of chunk c from the group-level rows (GEN only): TMA lands the raw Bn / Cn
+    // rows of this head's group in the K / Q tiles and gen_apply rewrites them in place.
+    // Thread (lane, warp w) owns the 16-byte pieces j = w and w + 8 of the rows lane,
+    // lane + 32, lane + 64, lane + 96.  The angle of (row, a) is the angle entering the chunk
+    // (f64, shared memory) plus an inclusive sum over the rows: a warp shuffle scan inside each
+    // block of 32 rows and a running prefix over the four blocks, which the same thread owns.
+    // this thread's angle velocities of the chunk that gen_apply rewrites next (loaded a
+    // chunk ahead, like the per-row scalars)
+    float4 velr[4][2];
+    auto load_vel = [&](int c) {
+        const int t0 = c * CS, nv = min(CS, T - t0), na = p.n_angles;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int j = wfull + 8 * q, row = lane + 32 * i;
-                vel[i][q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (4 * j < na && row < nv)
-                    vel[i][q] = __ldg(reinterpret_cast<const float4*>(
+                velr[i][q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (c < nchunks && 4 * j < na && row < nv)
+                    velr[i][q] = __ldg(reinterpret_cast<const float4*>(
                         p.angle_vel + (static_cast<long long>(b) * T + t0 + row) * na + 4 * j));
             }
-        float base[2][4], pre[2][4];
+    };
+    auto gen_apply = [&](int c, int buf) {
+        const int t0 = c * CS, nv = min(CS, T - t0);
+        const int na = p.n_angles;
+        constexpr double kTwoPi64 = 6.283185307179586, kInvTwoPi64 = 0.15915494309189535;
+        const bool rot0 = 4 * wfull < na, rot1 = 4 * (wfull + 8) < na;
+        float ang[4][2][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = lane + 32 * i;
+            const float dtr = row < nv ? dtv[row] : 0.0f;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                ang[i][q][0] = velr[i][q].x * dtr; ang[i][q][1] = velr[i][q].y * dtr;
+                ang[i][q][2] = velr[i][q].z * dtr; ang[i][q][3] = velr[i][q].w * dtr;
+            }
+        }
+        // inclusive sums over the 32 rows of each block: every value advances together
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    if (q ? rot1 : rot0) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float o = __shfl_up_sync(0xffffffffu, ang[i][q][e], m);
+                            if (lane >= m) ang[i][q][e] += o;
+                        }
+                    }
+        }
+        // entering angle + the blocks before; the chunk's total goes into the f64 carry
 #pragma unroll
         for (int q = 0; q < 2; ++q)
+            if (q ? rot1 : rot0) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int a = 4 * (wfull + 8 * q) + e;
-                base[q][e] = a < na ? static_cast<float>(carry[a]) : 0.0f;
-                pre[q][e] = 0.0f;
+                for (int e = 0; e < 4; ++e) {
+                    const int a = 4 * (wfull + 8 * q) + e;
+                    const double cin = carry[a];
+                    float run = static_cast<float>(cin), tot = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float bt = __shfl_sync(0xffffffffu, ang[i][q][e], 31);
+                        ang[i][q][e] += run;
+                        run += bt;
+                        tot += bt;
+                    }
+                    double sacc = cin + static_cast<double>(tot);
+                    sacc -= kTwoPi64 * floor(sacc * kInvTwoPi64);
+                    __syncwarp();
+                    if (lane == 0) carry[a] = sacc;
+                }
             }
-        asm volatile("cp.async.wait_all;" ::: "memory");  // this thread's own pieces have landed
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int row = lane + 32 * i;
             const bool rok = row < nv;
-            const float dtr = rok ? dtv[row] : 0.0f;
-            float sn[2][4], cs[2][4];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                if (4 * (wfull + 8 * q) < na) {
-                    const float vv[4] = {vel[i][q].x, vel[i][q].y, vel[i][q].z, vel[i][q].w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float v = vv[e] * dtr;
-#pragma unroll
-                        for (int m = 1; m < 32; m <<= 1) {
-                            const float o = __shfl_up_sync(0xffffffffu, v, m);
-                            if (lane >= m) v += o;
-                        }
-                        float ang = base[q][e] + pre[q][e] + v;
-                        pre[q][e] += __shfl_sync(0xffffffffu, v, 31);
-                        // to [-pi, pi] before the fast sine / cosine
-                        const float turns = rintf(ang * 0.15915494309189535f);
-                        ang = fmaf(turns, -6.2831854820251465f, ang);
-                        ang = fmaf(turns, 1.7484555e-7f, ang);
-                        __sincosf(ang, &sn[q][e], &cs[q][e]);
-                    }
-                }
-            }
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int j = wfull + 8 * q;
+                const bool rot = q ? rot1 : rot0;
+                float sn[4], cs[4];
+                if (rot) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // to [-pi, pi] before the fast sine / cosine
+                        float x = ang[i][q][e];
+                        const float turns = rintf(x * 0.15915494309189535f);
+                        x = fmaf(turns, -6.2831854820251465f, x);
+                        x = fmaf(turns, 1.7484555e-7f, x);
+                        __sincosf(x, &sn[e], &cs[e]);
+                    }
+                }
                 if (8 * j < nsv && rok) {
-                    const bool rot = 4 * j < na;
 #pragma unroll
                     for (int which = 0; which < 2; ++which) {
-                        uint4* pp = reinterpret_cast<uint4*>(smem + (which ? kQ : kK) + chunk_off(row, j, NS));
+                        uint4* pp = reinterpret_cast<uint4*>(smem + (which ? kQ0 : kK0) + buf * kQKStride +
+                                                             sw_chunk(row, j));
                         const uint4 raw = *pp;
                         const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
                         const float4 b0 = *reinterpret_cast<const float4*>(bias_sm + which * 128 + 8 * j);
@@ -365,7 +368,7 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
                             const float2 f = unpack2<Th>(rw[e]);
                             float v0 = f.x + bv[2 * e], v1 = f.y + bv[2 * e + 1];
                             if (rot) {
-                                const float r0 = cs[q][e] * v0 - sn[q][e] * v1, r1 = sn[q][e] * v0 + cs[q][e] * v1;
+                                const float r0 = cs[e] * v0 - sn[e] * v1, r1 = sn[e] * v0 + cs[e] * v1;
                                 v0 = r0; v1 = r1;
                             }
                             ow[e] = pack2<Th>(v0, v1);
@@ -375,61 +378,65 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
                 }
             }
         }
-        // fold this chunk's sums into the entering angle of the next one
-#pragma unroll
-        for (int q = 0; q < 2; ++q)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int a = 4 * (wfull + 8 * q) + e;
-                if (a < na) {
-                    double sacc = carry[a] + static_cast<double>(pre[q][e]);
-                    sacc -= kTwoPi64 * floor(sacc * kInvTwoPi64);
-                    __syncwarp();
-                    if (lane == 0) carry[a] = sacc;
-                }
-            }
     };
 
+    // One elected thread issues the five boxes of a chunk (Q and K: two 64-column sub-tiles
+    // each, V: one); rows past the end of the sequence and columns past the head's width
+    // arrive as zeros.
     auto issue_tiles = [&](int c) {
-        if (GEN) {
-            gen_issue(c);
-        } else {
-            issue_qk(Qg, kQ, c);
-            issue_qk(Kg, kK, c);
+        if (threadIdx.x == 0) {
+            const int buf = c & 1, t0 = c * CS;
+            const int hq = GEN ? h / (nh / p.ng) : h;
+            mbar_expect_tx(&full[buf], 2 * kQKStride + kVStride);
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                tma_load_4d(smem + kQ0 + buf * kQKStride + sub * kSwSub, &p.tm_q, &full[buf], 64 * sub, hq, t0, b);
+                tma_load_4d(smem + kK0 + buf * kQKStride + sub * kSwSub, &p.tm_k, &full[buf], 64 * sub, hq, t0, b);
+            }
+            tma_load_4d(smem + kV0 + buf * kVStride, &p.tm_v, &full[buf], 0, h, t0, b);
         }
-        issue_v(kV, c);
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    issue_tiles(0);
+    stage_scalars(0);
+    if (GEN) load_vel(0);
 
     for (int c = 0; c < nchunks; ++c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
-        const int t = t0 + tid;  // this thread's row
         const bool row_ok = tid < nv;
         const float* dA = vec;
         const float* scl = dA + 128;
         const float* gam = dA + 256;
-        const uint32_t tK = kK, tV = kV;
-        // ---- 1. this chunk's Q, K, V tiles (asynchronous copies) and per-row scalars ----
-        // (issuing chunk c + 1 during the epilogue of chunk c was measured: 5 % slower)
-        issue_tiles(c);
+        const uint32_t tQ = kQ0 + (c & 1) * kQKStride, tK = kK0 + (c & 1) * kQKStride, tV = kV0 + (c & 1) * kVStride;
+        // ---- 1. copies of the next chunk's tiles into the other buffers (their last readers,
+        //         the MMAs of chunk c - 1, have completed); per-row scalars; this chunk's tiles ----
+        if (c + 1 < nchunks) issue_tiles(c + 1);
         scalars(c, 0);
-        if (GEN) gen_apply(c);
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        fence_proxy_async();
+        ok = mbar_wait(&full[c & 1], (c >> 1) & 1, p.status) && ok;
+        if (GEN) {
+            gen_apply(c, c & 1);
+            fence_proxy_async();  // the rewritten K / Q pieces, before the tensor core reads them
+        }
         fence_before();
         __syncthreads();
+        // A proxy fence waits for this thread's outstanding asynchronous copies (measured:
+        // 1500 cycles when the staged scalars were issued ahead of one), so they start here,
+        // with the MMA wait and the mask stage between them and the next fence.
+        stage_scalars(c + 1);
         // ---- 2. G = Q K^T (and Y2 = Q S_in^T for c > 0) ----
         if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idG = instr_desc(fmt, 0, 0, 128), idY = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
             for (int k = 0; k < NS / 16; ++k)
-                mma(tmem + cG, desc_kmajor(sbase + kQ, k, NS), desc_kmajor(sbase + tK, k, NS), idG, k > 0);
+                mma(tmem + cG, desc_sw_k(sbase + tQ, k), desc_sw_k(sbase + tK, k), idG, k > 0);
             if (c > 0) {
 #pragma unroll
                 for (int k = 0; k < NS / 16; ++k)  // N = p, K = n
-                    mma(tmem + cY2, desc_kmajor(sbase + kQ, k, NS), desc_mnmajor(sbase + kS, k, HD), idY, k > 0);
+                    mma(tmem + cY2, desc_sw_k(sbase + tQ, k), desc_sw_mn(sbase + kS, k), idY, k > 0);
             }
+            // the y tile of the previous chunk (stored from the M tile) has been read out: every
+            // thread learns it through bars[0] before the mask stage rewrites M
+            tma_wait_read0();
             commit(&bars[0]);
         }
         ok = mbar_wait(&bars[0], c & 1, p.status) && ok;
@@ -441,14 +448,14 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
                 const float wt = row_ok ? ex2((dA[nv - 1] - dA[tid]) * kLog2e) * scl[tid] : 0.0f;
 #pragma unroll
                 for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(smem + tV + chunk_off(tid, j, HD));
+                    const uint4 v = *reinterpret_cast<const uint4*>(smem + tV + sw_chunk(tid, j));
                     uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         const float2 f = unpack2<Th>(w4[q4]);
                         w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
                     }
-                    *reinterpret_cast<uint4*>(smem + kVw + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    *reinterpret_cast<uint4*>(smem + kVw + sw_chunk(tid, j)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
             }
             const float* dAl = dA + 384;  // dA * log2(e)
@@ -482,14 +489,14 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) =
+                    *reinterpret_cast<uint4*>(smem + kM + sw_chunk(tid, q4 * 4 + j)) =
                         make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
             };
             for (int q4 = 2 * half; q4 < 2 * half + 2; ++q4) {
                 if (q4 > warp) {  // wholly above the diagonal for every row of this warp
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(smem + kM + chunk_off(tid, q4 * 4 + j, CS)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(smem + kM + sw_chunk(tid, q4 * 4 + j)) = make_uint4(0, 0, 0, 0);
                 } else if (q4 == warp) {
                     mask_block(std::true_type{}, q4);
                 } else {
@@ -508,16 +515,18 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         fence_proxy_async();
         fence_before();
         __syncthreads();
+        // register loads issued here have the longest run before the next proxy fence
+        if (GEN) load_vel(c + 1);
         // ---- 4. Y1 = M V ;  S^T += K^T (w o V) ----
         if (threadIdx.x == 0) {
             fence_after();
             const uint32_t idY = instr_desc(fmt, 0, 1, 64), idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // N = p, K = s
-                mma(tmem + cY1, desc_kmajor(sbase + kM, k, CS), desc_mnmajor(sbase + tV, k, HD), idY, k > 0);
+                mma(tmem + cY1, desc_sw_k(sbase + kM, k), desc_sw_mn(sbase + tV, k), idY, k > 0);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // M = n, N = p, K = t
-                mma(tmem + cS, desc_mnmajor(sbase + tK, k, NS), desc_mnmajor(sbase + kVw, k, HD), idS, c > 0 || k > 0);
+                mma(tmem + cS, desc_sw_mn(sbase + tK, k), desc_sw_mn(sbase + kVw, k), idS, c > 0 || k > 0);
             commit(&bars[1]);
         }
         ok = mbar_wait(&bars[1], c & 1, p.status) && ok;
@@ -525,7 +534,6 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         // ---- 5. epilogue: y row; 16-bit copy of the new state for the next chunk ----
         {
             const float e_t = ex2(dA[tid] * kLog2e);
-            const long long y_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
             const int q2 = half;
             float y1[32], y2[32];
             if (c > 0) {
@@ -535,20 +543,19 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             } else {
                 tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
             }
-            if (row_ok) {
+            // y leaves through the M tile (free once Y1 is done) and one TMA store, which
+            // clips the rows past T and the columns past headdim
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (q2 * 32 + 8 * j < hdv)
-                        *reinterpret_cast<uint4*>(yg + y_row + q2 * 32 + 8 * j) =
-                        make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
-                                   pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
-            }
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(smem + kM + sw_chunk(tid, q2 * 4 + j)) =
+                    make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
+                               pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
             float sv[32];
             tmem_ld32(lane_addr + cS + q2 * 32, sv);
             if (c + 1 < nchunks) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(smem + kS + chunk_off(tid, q2 * 4 + j, HD)) =
+                    *reinterpret_cast<uint4*>(smem + kS + sw_chunk(tid, q2 * 4 + j)) =
                         make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
                                    pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
             } else if (p.ssm_state) {  // final state [b, h, p, n], n = tid
@@ -558,9 +565,14 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
                         p.ssm_state[((static_cast<long long>(b) * nh + h) * hdv + q2 * 32 + i) * nsv + tid] = sv[i];
             }
         }
+        fence_proxy_async();
         fence_before();
         __syncthreads();
         fence_after();
+        if (threadIdx.x == 0) {
+            tma_store_4d(&p.tm_y, smem + kM, 0, h, t0, b);
+            tma_commit();
+        }
     }
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
@@ -570,7 +582,8 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
             const int lr = T - 1 - (nchunks - 1) * CS;
             if (p.k_state && half == 0 && tid < nsv)
                 p.k_state[(static_cast<long long>(b) * nh + h) * nsv + tid] =
-                    to_f(*reinterpret_cast<const Th*>(smem + kK + chunk_off(lr, tid >> 3, NS) + (tid & 7) * 2));
+                    to_f(*reinterpret_cast<const Th*>(smem + kK0 + ((nchunks - 1) & 1) * kQKStride +
+                                                     sw_chunk(lr, tid >> 3) + (tid & 7) * 2));
             if (p.angle_state && threadIdx.x < p.n_angles)
                 p.angle_state[(static_cast<long long>(b) * nh + h) * p.n_angles + threadIdx.x] =
                     static_cast<float>(carry[threadIdx.x]);
@@ -579,6 +592,7 @@ __global__ void __launch_bounds__(256, 2) m3_ssd_fwd_tc_kernel(const M3Params p)
         if (p.v_state && half == 0 && tid < hdv)
             p.v_state[(static_cast<long long>(b) * nh + h) * hdv + tid] = to_f(xg[last * nh * hdv + h * hdv + tid]);
     }
+    if (threadIdx.x == 0) tma_wait_all0();
     __syncthreads();
     if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -658,6 +672,11 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
                                               "storage, headdim <= 64, d_state <= 128, multiples of 8, no carried "
                                               "state, 16-byte aligned tensors)");
     if (tensor_core) {
+        const bool maps = make_tmap_head_tile(c, &p.tm_q, a.dtype, gen ? a.Cn : a.Q, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
+                          make_tmap_head_tile(c, &p.tm_k, a.dtype, gen ? a.Bn : a.K, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
+                          make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B) &&
+                          make_tmap_head_tile(c, &p.tm_y, a.dtype, a.y, a.hd, a.nh, a.T, a.B);
+        if (!maps) return fail(c, MAMBA_B200_ERR_CUDA, "m3_ssd_fwd: tensor map encoding failed");
         dim3 grid(a.nh, a.B);
         if (a.dtype == MAMBA_B200_BF16) {
             if (gen) tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, true><<<grid, 256, tc::kSmem, st>>>(p);

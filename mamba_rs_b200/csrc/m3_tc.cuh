@@ -116,6 +116,10 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
                  "r"(valid ? 16u : 0u)
                  : "memory");
 }
+// 4-byte asynchronous copy global -> shared.
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -125,6 +129,29 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int k, int C) {
 }
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int k, int C) {
     return smem_desc(tile + k * 2 * (C >> 3) * 128, (C >> 3) * 128, 128);
+}
+
+// ---- 128-byte-swizzled tiles (what a TMA copy with CU_TENSOR_MAP_SWIZZLE_128B writes) ----
+// A tile of R rows x 64 16-bit columns is R rows of 128 bytes, the 16-byte piece j of row r
+// stored at piece j ^ (r % 8); a 128-column tile is two such sub-tiles, kSwSub bytes apart
+// (128 rows).  Descriptor fields found by comparing every operand form against a host
+// product: layout type 2; stride byte offset 1024 (eight rows); a K-major operand advances
+// 32 bytes per 16-element K step inside a sub-tile (the leading byte offset is unused); an
+// MN-major operand advances 2048 bytes (sixteen rows) per K step and its leading byte offset
+// is the distance between the 64-column sub-tiles.
+constexpr uint32_t kSwSub = 16384;
+__device__ __forceinline__ uint32_t sw_chunk(int r, int j) {
+    return static_cast<uint32_t>((j >> 3) * kSwSub + r * 128 + (((j & 7) ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ uint64_t smem_desc_sw(uint32_t addr, uint32_t lbo_bytes) {
+    return static_cast<uint64_t>((addr & 0x3FFFF) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t desc_sw_k(uint32_t tile, int k) {
+    return smem_desc_sw(tile + (k >> 2) * kSwSub + (k & 3) * 32, 16);
+}
+__device__ __forceinline__ uint64_t desc_sw_mn(uint32_t tile, int k) {
+    return smem_desc_sw(tile + k * 2048, kSwSub);
 }
 
 }  // namespace tc
