@@ -23,7 +23,9 @@ namespace mb200 {
 
 struct M3Params {
     // tensor-core kernel: Q (or Cn), K (or Bn) and x as [128 x 64] swizzled sub-tile maps
-    CUtensorMap tm_q, tm_k, tm_v, tm_y;
+    CUtensorMap tm_q, tm_k, tm_v;
+    CUtensorMap tm_adt, tm_dt, tm_trap;  // [B,T,nh] f32, boxes of 4 heads x 129 rows
+    int sc_tma;                          // 1: the three maps above are valid (nheads % 4 == 0)
     const void *x, *K, *Q;
     const float *dt, *trap, *adt, *Dh;
     void* y;
@@ -138,8 +140,10 @@ constexpr uint32_t kVec = 212992;  // f32 dA[128], scale[128], gamma[128], dA*lo
 constexpr uint32_t kCarry = kVec + 5 * 128 * 4, kBias = kCarry + 64 * 8;
 // per-row adt, dt, trap of a chunk (dt and trap with the row after it), two buffers,
 // filled by 4-byte asynchronous copies
-constexpr uint32_t kStage = kBias + 2 * 128 * 4, kStageBuf = 3 * 132 * 4;
-constexpr uint32_t kBar = kStage + 2 * kStageBuf, kTmemSlot = kBar + 32;
+// [3][129 rows][4 heads] f32; a TMA destination has to start on a 128-byte boundary
+constexpr uint32_t kStage = kBias + 2 * 128 * 4, kStageArr = 17 * 128;
+static_assert(kStage % 128 == 0 && kStageArr >= 129 * 16, "scalar staging");
+constexpr uint32_t kBar = kStage + 3 * kStageArr + 16, kTmemSlot = kBar + 48;
 constexpr uint32_t kSmem = kTmemSlot + 16;
 // TMEM columns: G; Y1; Y2; S^T.
 constexpr uint32_t cG = 0, cY1 = 256, cY2 = 320, cS = 384, kTmemCols = 512;
@@ -174,6 +178,7 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
         mbar_init(&bars[1], 1);
         mbar_init(&full[0], 1);
         mbar_init(&full[1], 1);
+        mbar_init(bars + 4, 1);
         fence_barrier_init();
     }
     float* dtv = vec + 512;
@@ -202,41 +207,59 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);  // this warp's 32 lanes
 
     const Th* xg = static_cast<const Th*>(p.x);
+    Th* yg = static_cast<Th*>(p.y);
     const Th* Kg = static_cast<const Th*>(p.K);
     const float Dv = p.Dh[h];
     const int nchunks = (T + CS - 1) / CS;
     bool ok = true;
 
     // Per-row scalars of chunk c into stage `st`: inclusive cumsum of adt, scale, gamma.
-    // Per-row scalars travel a chunk ahead as 4-byte asynchronous copies into shared memory:
-    // with nheads > 1 they are 128-byte-strided words, and as register loads they were
-    // drained by every proxy fence of the chunk (0.18 ms of 0.45 ms at 32 heads).
+    // Per-row adt, dt, trap of the next chunk (dt and trap with the row after it) are staged in
+    // shared memory while the current chunk runs.  As register loads they were drained by every
+    // proxy fence of the chunk (0.18 ms of 0.45 ms at 32 heads, where they are 128-byte-strided
+    // words); a fence waits for 4-byte asynchronous copies too.  TMA copies are not waited for:
+    // with nheads % 4 == 0 one thread fetches [129 rows x 4 heads] boxes; otherwise the copies
+    // are issued where the next fence is furthest away.
+    uint64_t* scf = bars + 4;
+    const int hcol = h & 3;
     auto stage_scalars = [&](int c) {
-        if (c < nchunks && threadIdx.x <= CS) {
-            float* st = reinterpret_cast<float*>(smem + kStage + (c & 1) * kStageBuf);
-            const int r = threadIdx.x, t = c * CS + r;
-            const long long th = (static_cast<long long>(b) * T + t) * nh + h;
-            if (t < T) {
-                if (r < CS) cp_async4(st + r, p.adt + th);
-                cp_async4(st + 132 + r, p.dt + th);
-                cp_async4(st + 264 + r, p.trap + th);
-            } else {
-                if (r < CS) st[r] = 0.0f;
-                st[132 + r] = 0.0f;
-                st[264 + r] = 0.0f;
+        if (c >= nchunks) return;
+        if (p.sc_tma) {
+            if (threadIdx.x == 0) {
+                mbar_expect_tx(scf, 3 * 129 * 16);
+                tma_load_3d(smem + kStage, &p.tm_adt, scf, h & ~3, c * CS, b);
+                tma_load_3d(smem + kStage + kStageArr, &p.tm_dt, scf, h & ~3, c * CS, b);
+                tma_load_3d(smem + kStage + 2 * kStageArr, &p.tm_trap, scf, h & ~3, c * CS, b);
             }
+        } else {
+            if (threadIdx.x <= CS) {
+                float* st = reinterpret_cast<float*>(smem + kStage) + threadIdx.x * 4 + hcol;
+                const int t = c * CS + threadIdx.x;
+                const long long th = (static_cast<long long>(b) * T + t) * nh + h;
+                if (t < T) {
+                    cp_async4(st, p.adt + th);
+                    cp_async4(st + kStageArr / 4, p.dt + th);
+                    cp_async4(st + 2 * kStageArr / 4, p.trap + th);
+                } else {
+                    st[0] = st[kStageArr / 4] = st[2 * kStageArr / 4] = 0.0f;
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     auto scalars = [&](int c, int st) {
         float* dA = vec + st * 384;
         float* scl = dA + 128;
         float* gam = dA + 256;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // every thread's staged words of this chunk are in shared memory
-        const float* stg = reinterpret_cast<const float*>(smem + kStage + (c & 1) * kStageBuf);
-        const float a = stg[tid], dtr = stg[132 + tid], g = dtr * stg[264 + tid];
-        const float s = g + stg[132 + tid + 1] * (1.0f - stg[264 + tid + 1]);
+        if (p.sc_tma) {
+            ok = mbar_wait(scf, c & 1, p.status) && ok;
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();  // every thread's staged words of this chunk are in shared memory
+        }
+        const float* stg = reinterpret_cast<const float*>(smem + kStage) + hcol;
+        const float a = stg[tid * 4], dtr = stg[kStageArr / 4 + tid * 4], g = dtr * stg[2 * kStageArr / 4 + tid * 4];
+        const float s = g + stg[kStageArr / 4 + tid * 4 + 4] * (1.0f - stg[2 * kStageArr / 4 + tid * 4 + 4]);
         float run = a;
 #pragma unroll
         for (int m = 1; m < 32; m <<= 1) {
@@ -434,9 +457,6 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
                 for (int k = 0; k < NS / 16; ++k)  // N = p, K = n
                     mma(tmem + cY2, desc_sw_k(sbase + tQ, k), desc_sw_mn(sbase + kS, k), idY, k > 0);
             }
-            // the y tile of the previous chunk (stored from the M tile) has been read out: every
-            // thread learns it through bars[0] before the mask stage rewrites M
-            tma_wait_read0();
             commit(&bars[0]);
         }
         ok = mbar_wait(&bars[0], c & 1, p.status) && ok;
@@ -543,13 +563,11 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
             } else {
                 tmem_ld32(lane_addr + cY1 + q2 * 32, y1);
             }
-            // y leaves through the M tile (free once Y1 is done) and one TMA store, which
-            // clips the rows past T and the columns past headdim
+            uint4 yo[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                *reinterpret_cast<uint4*>(smem + kM + sw_chunk(tid, q2 * 4 + j)) =
-                    make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
-                               pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
+                yo[j] = make_uint4(pack2<Th>(y1[8 * j], y1[8 * j + 1]), pack2<Th>(y1[8 * j + 2], y1[8 * j + 3]),
+                                   pack2<Th>(y1[8 * j + 4], y1[8 * j + 5]), pack2<Th>(y1[8 * j + 6], y1[8 * j + 7]));
             float sv[32];
             tmem_ld32(lane_addr + cS + q2 * 32, sv);
             if (c + 1 < nchunks) {
@@ -564,15 +582,19 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
                     if (q2 * 32 + i < hdv && tid < nsv)
                         p.ssm_state[((static_cast<long long>(b) * nh + h) * hdv + q2 * 32 + i) * nsv + tid] = sv[i];
             }
+            fence_proxy_async();  // the state copy, before the next chunk's Y2 reads it
+            // y rows leave after the fence: a proxy fence waits for the thread's outstanding
+            // global stores too, and the next one is most of a chunk away
+            if (row_ok) {
+                Th* yrow = yg + (static_cast<long long>(b) * T + t0 + tid) * nh * hdv + h * hdv + q2 * 32;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (q2 * 32 + 8 * j < hdv) *reinterpret_cast<uint4*>(yrow + 8 * j) = yo[j];
+            }
         }
-        fence_proxy_async();
         fence_before();
         __syncthreads();
         fence_after();
-        if (threadIdx.x == 0) {
-            tma_store_4d(&p.tm_y, smem + kM, 0, h, t0, b);
-            tma_commit();
-        }
     }
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
@@ -592,7 +614,6 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
         if (p.v_state && half == 0 && tid < hdv)
             p.v_state[(static_cast<long long>(b) * nh + h) * hdv + tid] = to_f(xg[last * nh * hdv + h * hdv + tid]);
     }
-    if (threadIdx.x == 0) tma_wait_all0();
     __syncthreads();
     if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -674,9 +695,12 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
     if (tensor_core) {
         const bool maps = make_tmap_head_tile(c, &p.tm_q, a.dtype, gen ? a.Cn : a.Q, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
                           make_tmap_head_tile(c, &p.tm_k, a.dtype, gen ? a.Bn : a.K, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
-                          make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B) &&
-                          make_tmap_head_tile(c, &p.tm_y, a.dtype, a.y, a.hd, a.nh, a.T, a.B);
+                          make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B);
         if (!maps) return fail(c, MAMBA_B200_ERR_CUDA, "m3_ssd_fwd: tensor map encoding failed");
+        p.sc_tma = a.nh % 4 == 0 &&
+                   make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
+                   make_tmap_3d(c, &p.tm_dt, MAMBA_B200_F32, a.dt, a.nh, a.nh, a.T, a.B, 4, 129) &&
+                   make_tmap_3d(c, &p.tm_trap, MAMBA_B200_F32, a.trap, a.nh, a.nh, a.T, a.B, 4, 129);
         dim3 grid(a.nh, a.B);
         if (a.dtype == MAMBA_B200_BF16) {
             if (gen) tc::m3_ssd_fwd_tc_kernel<__nv_bfloat16, true><<<grid, 256, tc::kSmem, st>>>(p);

@@ -116,6 +116,10 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
                  "r"(valid ? 16u : 0u)
                  : "memory");
 }
+// One arrival on an mbarrier of this CTA (release at CTA scope).
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // 4-byte asynchronous copy global -> shared.
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
