@@ -31,6 +31,10 @@ namespace mb200 {
 constexpr int kM3C = 32;  // chunk length of the backward
 
 struct M3BwdParams {
+    // tensor-core kernel: adt, dt, trap [B,T,nh] f32 as boxes of 4 heads x 129 rows (valid when
+    // sc_tma; needs nheads % 4 == 0)
+    CUtensorMap tm_adt, tm_dt, tm_trap;
+    int sc_tma;
     const void *x, *K, *Q, *dy;
     const float *dt, *trap, *adt, *Dh;
     void* dx;
@@ -324,12 +328,17 @@ constexpr int CS = 128, HD = 64, NS = 128;
 constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kDS = 114688, kM1 = 131072,
                    kM2 = 163840, kEdY = 196608, kVec = 212992;
 // f32 vectors: dA, scl, gam, red (scratch), gdv, pdv, part[5], dA*log2(e)
-constexpr uint32_t kBar = kVec + 12 * 128 * 4, kTmemSlot = kBar + 32, kSmem = kTmemSlot + 16;
+// staging of the per-row scalars of one chunk: [3][129 rows][4 heads] f32, each array on a
+// 128-byte boundary (TMA destinations)
+constexpr uint32_t kStage = kVec + 12 * 128 * 4, kStageArr = 17 * 128;
+static_assert(kStage % 128 == 0 && kStageArr >= 129 * 16, "scalar staging");
+constexpr uint32_t kBar = kStage + 3 * kStageArr, kTmemSlot = kBar + 48, kSmem = kTmemSlot + 16;
+static_assert(kSmem <= 227 * 1024, "shared memory");
 constexpr uint32_t c0 = 0, c1 = 128, c2 = 256, c3 = 384, cDS = 448, kTmemCols = 512;
 constexpr uint32_t kStateTile = NS * HD * 2;  // bytes of one 16-bit state copy
 
 template <typename Th>
-__global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p) {
+__global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constant__ M3BwdParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // two threads per step: (row tid, half) share TMEM lane tid and split its columns
     const int tid = threadIdx.x & 127, half = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3, lane = tid & 31;
@@ -351,7 +360,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     const uint32_t sbase = smem_u32(smem);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
         fence_barrier_init();
     }
     if (threadIdx.x < 32) {
@@ -379,11 +388,33 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
     bool ok = true;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
+    // The per-row adt, dt, trap of a chunk come as three TMA boxes issued before the tile
+    // copies (so they land while those are being issued) instead of 128-byte-strided register
+    // loads with their latency exposed; without the maps (nheads % 4 != 0) the loads remain.
+    uint32_t scph = 0;
+    const int hcol = h & 3;
+    auto issue_scalars = [&](int t0) {
+        if (p.sc_tma && threadIdx.x == 0) {
+            mbar_expect_tx(&bars[4], 3 * 129 * 16);
+            tma_load_3d(smem + kStage, &p.tm_adt, &bars[4], h & ~3, t0, b);
+            tma_load_3d(smem + kStage + kStageArr, &p.tm_dt, &bars[4], h & ~3, t0, b);
+            tma_load_3d(smem + kStage + 2 * kStageArr, &p.tm_trap, &bars[4], h & ~3, t0, b);
+        }
+    };
     // per-row scalars of chunk c -> dA (inclusive cumsum), scl, gam in shared memory
     auto load_scalars = [&](int t0, int nv, float& run_o, float& g_o, float& s_o) {
         const int t = t0 + tid;
         float a = 0.0f, g = 0.0f, s = 0.0f;
-        if (tid < nv) {
+        if (p.sc_tma) {
+            ok = mbar_wait(&bars[4], scph, p.status) && ok;
+            scph ^= 1;
+            const float* stg = reinterpret_cast<const float*>(smem + kStage) + tid * 4 + hcol;
+            if (tid < nv) {  // rows past T arrive as zeros
+                a = stg[0];
+                g = stg[kStageArr / 4] * stg[2 * kStageArr / 4];
+                s = g + stg[kStageArr / 4 + 4] * (1.0f - stg[2 * kStageArr / 4 + 4]);
+            }
+        } else if (tid < nv) {
             const long long th = (static_cast<long long>(b) * T + t) * nh + h;
             a = p.adt[th];
             g = p.dt[th] * p.trap[th];
@@ -444,6 +475,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const bool last = c + 1 == nc;
         float run = 0.0f, g = 0.0f, s = 0.0f;
         if (!last) {
+            issue_scalars(t0);
             issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
             issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
             cp_async_commit();
@@ -509,6 +541,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const M3BwdParams p)
         const bool row_ok = tid < nv;
         const bool has_sin = c > 0;
         // ---- loads (asynchronous, 8 rows x 64 bytes per warp instruction) under the scalars ----
+        issue_scalars(t0);
         issue_rows(Qg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kQ, NS, nsv, nv);
         issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
         issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
@@ -988,6 +1021,10 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     dim3 grid(a.nh, a.B);
     const size_t smem = m3_bwd_smem(a.hd, a.N);
     if (tensor_core) {
+        p.sc_tma = a.nh % 4 == 0 &&
+                   make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
+                   make_tmap_3d(c, &p.tm_dt, MAMBA_B200_F32, a.dt, a.nh, a.nh, a.T, a.B, 4, 129) &&
+                   make_tmap_3d(c, &p.tm_trap, MAMBA_B200_F32, a.trap, a.nh, a.nh, a.T, a.B, 4, 129);
         if (a.dtype == MAMBA_B200_F16) tcb::m3_ssd_bwd_tc_kernel<__half><<<grid, 256, tcb::kSmem, st>>>(p);
         else tcb::m3_ssd_bwd_tc_kernel<__nv_bfloat16><<<grid, 256, tcb::kSmem, st>>>(p);
     } else if (a.dtype == MAMBA_B200_F32) m3_ssd_bwd_kernel<float><<<grid, 256, smem, st>>>(p);
