@@ -35,6 +35,7 @@ struct M3BwdParams {
     // sc_tma; needs nheads % 4 == 0)
     CUtensorMap tm_adt, tm_dt, tm_trap;
     int sc_tma;
+    int wide_st;  // dK and dQ are 32-byte aligned: their rows leave as 256-bit stores
     const void *x, *K, *Q, *dy;
     const float *dt, *trap, *adt, *Dh;
     void* dx;
@@ -323,6 +324,19 @@ __global__ void m3_bwd_finish_kernel(const M3BwdParams p) {
 // so results carry 16-bit rounding like the forward's tensor-core path.
 namespace tcb {
 using namespace tc;
+
+// Eight consecutive floats: one 256-bit store (a whole 32-byte sector per request) when the
+// destination allows it, else two 128-bit stores.
+__device__ __forceinline__ void store8(float* dst, const float* o, bool wide) {
+    if (wide) {
+        asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "f"(o[0]), "f"(o[1]), "f"(o[2]),
+                     "f"(o[3]), "f"(o[4]), "f"(o[5]), "f"(o[6]), "f"(o[7])
+                     : "memory");
+    } else {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+}
 
 constexpr int CS = 128, HD = 64, NS = 128;
 constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kDS = 114688, kM1 = 131072,
@@ -771,11 +785,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                             o[2 * u] = fmaf(gp, f.x, av[8 * j + 2 * u]);
                             o[2 * u + 1] = fmaf(gp, f.y, av[8 * j + 2 * u + 1]);
                         }
-                        if (q4 * 32 + 8 * j < nsv) {
-                            float4* dst = reinterpret_cast<float4*>(p.dQ + qk_row + q4 * 32 + 8 * j);
-                            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-                            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-                        }
+                        if (q4 * 32 + 8 * j < nsv) store8(p.dQ + qk_row + q4 * 32 + 8 * j, o, p.wide_st != 0);
                     }
                 }
             }
@@ -823,6 +833,23 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         }
         wait_bar(2);
         // ---- epilogue 3 ----
+        // 16-bit copy of the new dS for the next (earlier) chunk
+        if (c > 0) {
+            {
+                const int q2 = half;
+                float sv[32];
+                tmem_ld32(lane_addr + cDS + q2 * 32, sv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(smem + kDS + chunk_off(tid, q2 * 4 + j, HD)) =
+                        make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
+                                   pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
+            }
+        }
+        // The proxy fence this copy needs comes before the dK rows are stored: a fence waits for
+        // the thread's outstanding global stores, and stored after it the 64 KB of dK drain
+        // under the next chunk's tile copies instead of at the end of this one.
+        fence_proxy_async();
         float zw = 0.0f;  // w_s <K_s, U_s>
         {
             const float gp = g_t * pd;
@@ -852,25 +879,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                         o[2 * u] = o0;
                         o[2 * u + 1] = o1;
                     }
-                    if (row_ok && q4 * 32 + 8 * j < nsv) {
-                        float4* dst = reinterpret_cast<float4*>(p.dK + qk_row + q4 * 32 + 8 * j);
-                        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-                        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-                    }
+                    if (row_ok && q4 * 32 + 8 * j < nsv) store8(p.dK + qk_row + q4 * 32 + 8 * j, o, p.wide_st != 0);
                 }
-            }
-        }
-        // 16-bit copy of the new dS for the next (earlier) chunk
-        if (c > 0) {
-            {
-                const int q2 = half;
-                float sv[32];
-                tmem_ld32(lane_addr + cDS + q2 * 32, sv);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(smem + kDS + chunk_off(tid, q2 * 4 + j, HD)) =
-                        make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
-                                   pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
             }
         }
         // ---- per-step scalars ----
@@ -906,7 +916,6 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             dD_acc += pd;
         }
         has_ds = true;
-        fence_proxy_async();
         fence_before();
         __syncthreads();
         fence_after();
@@ -1021,6 +1030,7 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     dim3 grid(a.nh, a.B);
     const size_t smem = m3_bwd_smem(a.hd, a.N);
     if (tensor_core) {
+        p.wide_st = (reinterpret_cast<uintptr_t>(a.dK) | reinterpret_cast<uintptr_t>(a.dQ)) % 32 == 0;
         p.sc_tma = a.nh % 4 == 0 &&
                    make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
                    make_tmap_3d(c, &p.tm_dt, MAMBA_B200_F32, a.dt, a.nh, a.nh, a.T, a.B, 4, 129) &&
