@@ -26,6 +26,7 @@ struct M3Params {
     CUtensorMap tm_q, tm_k, tm_v;
     CUtensorMap tm_adt, tm_dt, tm_trap;  // [B,T,nh] f32, boxes of 4 heads x 129 rows
     int sc_tma;                          // 1: the three maps above are valid (nheads % 4 == 0)
+    int wide_y;                          // 1: y rows leave as 256-bit stores
     const void *x, *K, *Q;
     const float *dt, *trap, *adt, *Dh;
     void* y;
@@ -587,9 +588,15 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
             // global stores too, and the next one is most of a chunk away
             if (row_ok) {
                 Th* yrow = yg + (static_cast<long long>(b) * T + t0 + tid) * nh * hdv + h * hdv + q2 * 32;
+                if (p.wide_y) {  // headdim a multiple of 16, y 32-byte aligned
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (q2 * 32 + 8 * j < hdv) *reinterpret_cast<uint4*>(yrow + 8 * j) = yo[j];
+                    for (int j = 0; j < 4; j += 2)
+                        if (q2 * 32 + 8 * j < hdv) store32b(yrow + 8 * j, yo[j], yo[j + 1], true);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (q2 * 32 + 8 * j < hdv) *reinterpret_cast<uint4*>(yrow + 8 * j) = yo[j];
+                }
             }
         }
         fence_before();
@@ -697,6 +704,7 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
                           make_tmap_head_tile(c, &p.tm_k, a.dtype, gen ? a.Bn : a.K, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
                           make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B);
         if (!maps) return fail(c, MAMBA_B200_ERR_CUDA, "m3_ssd_fwd: tensor map encoding failed");
+        p.wide_y = a.hd % 16 == 0 && reinterpret_cast<uintptr_t>(a.y) % 32 == 0;
         p.sc_tma = a.nh % 4 == 0 &&
                    make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
                    make_tmap_3d(c, &p.tm_dt, MAMBA_B200_F32, a.dt, a.nh, a.nh, a.T, a.B, 4, 129) &&

@@ -36,6 +36,7 @@ struct M3BwdParams {
     CUtensorMap tm_adt, tm_dt, tm_trap;
     int sc_tma;
     int wide_st;  // dK and dQ are 32-byte aligned: their rows leave as 256-bit stores
+    int wide_dx;  // the same for dx (headdim a multiple of 16)
     const void *x, *K, *Q, *dy;
     const float *dt, *trap, *adt, *Dh;
     void* dx;
@@ -795,6 +796,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 float av[32];
                 tmem_ld32(lane_addr + c3 + q2 * 32, av);
                 if (row_ok) {
+                    uint4 ox[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint4 yv = *reinterpret_cast<const uint4*>(smem + kDY + chunk_off(tid, q2 * 4 + j, HD));
@@ -805,8 +807,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                             const float2 f = unpack2<Th>(w4[u]);
                             o[u] = pack2<Th>(fmaf(dcoef, f.x, av[8 * j + 2 * u]), fmaf(dcoef, f.y, av[8 * j + 2 * u + 1]));
                         }
-                        if (q2 * 32 + 8 * j < hdv)
-                            *reinterpret_cast<uint4*>(dxg + x_row + q2 * 32 + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+                        ox[j] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    if (p.wide_dx) {  // headdim a multiple of 16, dx 32-byte aligned
+#pragma unroll
+                        for (int j = 0; j < 4; j += 2)
+                            if (q2 * 32 + 8 * j < hdv) store32b(dxg + x_row + q2 * 32 + 8 * j, ox[j], ox[j + 1], true);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (q2 * 32 + 8 * j < hdv) *reinterpret_cast<uint4*>(dxg + x_row + q2 * 32 + 8 * j) = ox[j];
                     }
                 }
             }
@@ -1031,6 +1041,7 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
     const size_t smem = m3_bwd_smem(a.hd, a.N);
     if (tensor_core) {
         p.wide_st = (reinterpret_cast<uintptr_t>(a.dK) | reinterpret_cast<uintptr_t>(a.dQ)) % 32 == 0;
+        p.wide_dx = a.hd % 16 == 0 && reinterpret_cast<uintptr_t>(a.dx) % 32 == 0;
         p.sc_tma = a.nh % 4 == 0 &&
                    make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
                    make_tmap_3d(c, &p.tm_dt, MAMBA_B200_F32, a.dt, a.nh, a.nh, a.T, a.B, 4, 129) &&

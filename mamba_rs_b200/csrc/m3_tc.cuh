@@ -116,6 +116,18 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
                  "r"(valid ? 16u : 0u)
                  : "memory");
 }
+// Thirty-two consecutive bytes: one 256-bit store (a whole sector per request) when the
+// destination is 32-byte aligned, else two 128-bit stores.
+__device__ __forceinline__ void store32b(void* dst, const uint4& a, const uint4& b, bool wide) {
+    if (wide) {
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(a.x), "r"(a.y), "r"(a.z),
+                     "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                     : "memory");
+    } else {
+        reinterpret_cast<uint4*>(dst)[0] = a;
+        reinterpret_cast<uint4*>(dst)[1] = b;
+    }
+}
 // One arrival on an mbarrier of this CTA (release at CTA scope).
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
