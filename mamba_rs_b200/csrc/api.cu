@@ -62,6 +62,7 @@ int m1_bwd_configure(Ctx* c);   // m1_bwd.cu
 int m3_configure(Ctx* c);       // m3_ssd.cu
 int m3_bwd_configure(Ctx* c);   // m3_ssd_bwd.cu
 int norm_configure(Ctx* c);     // norm.cu
+int conv_configure(Ctx* c);     // m1_step_conv.cu
 int train_ops_configure(Ctx* c);  // train_ops.cu
 
 }  // namespace mb200
@@ -101,6 +102,8 @@ extern "C" MAMBA_B200_API int mamba_b200_init(int device, void** handle) {
     rc = m3_bwd_configure(c);
     if (rc) return rc;
     rc = norm_configure(c);
+    if (rc) return rc;
+    rc = conv_configure(c);
     if (rc) return rc;
     rc = train_ops_configure(c);
     if (rc) return rc;

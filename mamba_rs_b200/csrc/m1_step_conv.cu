@@ -466,6 +466,142 @@ __global__ void __launch_bounds__(64) conv1d_bwd_vec_kernel(const ConvParams p) 
     }
 }
 
+// ---------------------------------------------------------------------------
+// conv1d + SiLU backward from shared-memory tiles (16-bit storage, d_conv <= 4, rows on
+// 16-byte boundaries).  The register kernels above are bound by instruction issue and load
+// latency (146 warp-instructions per step of two channels, each thread waiting on its own
+// 4-byte loads); here a CTA of 128 threads first brings the x and d_u rows of its 64 steps
+// (plus the halo) into shared memory with 16-byte loads that are all in flight together, then
+// thread = channel walks the steps out of shared memory with the same arithmetic in the same
+// order, and d_x leaves through a tile and 16-byte stores.
+// ---------------------------------------------------------------------------
+constexpr int kConvTileD = 128;
+constexpr int kConvTileXRows = kConvTT + 2 * kConvKV - 1;  // x[t0 - K .. t1 + K - 2]
+constexpr int kConvTileGRows = kConvTT + kConvKV - 1;      // d_u[t0 .. t1 + K - 2]
+template <typename Tact>
+constexpr size_t conv_tile_smem() {
+    return sizeof(Tact) * kConvTileD * (kConvTileXRows + kConvTileGRows + kConvTT) + sizeof(float) * kConvKV * kConvTileD;
+}
+
+template <typename Tact>
+__global__ void __launch_bounds__(kConvTileD) conv1d_bwd_tile_kernel(const ConvParams p) {
+    static_assert(sizeof(Tact) == 2, "16-bit storage");
+    constexpr int KV = kConvKV, DT = kConvTileD, PIECES = DT / 8;  // 16-byte pieces per row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Tact* xs = reinterpret_cast<Tact*>(smem_raw);            // [kConvTileXRows][DT], row r = step xt0 + r
+    Tact* gs = xs + kConvTileXRows * DT;                     // [kConvTileGRows][DT], row r = step t0 + r
+    Tact* dxs = gs + kConvTileGRows * DT;                    // [kConvTT][DT]
+    float* xneg = reinterpret_cast<float*>(dxs + kConvTT * DT);  // [K][DT]: x[-K .. -1] (chunk 0 only)
+    const int d0 = blockIdx.x * DT, chunk = blockIdx.y, t0 = chunk * kConvTT, b = blockIdx.z;
+    const int K = p.K, T = p.T, D = p.D;
+    const int t1 = min(T, t0 + kConvTT), t_start = min(T - 1, t1 + K - 2);
+    // row r of xs is step xt0 + r; rows of negative steps (first chunk) stay unused
+    const int xt0 = t0 - K, nx = t_start - xt0 + 1, ng = t_start - t0 + 1;
+    const Tact* xb = static_cast<const Tact*>(p.x) + static_cast<long long>(b) * T * p.ld_x + d0;
+    const Tact* gb = static_cast<const Tact*>(p.du) + static_cast<long long>(b) * T * p.ld_du + d0;
+    Tact* dxb = static_cast<Tact*>(p.dx) + static_cast<long long>(b) * T * p.ld_dx + d0;
+    const int tid = threadIdx.x;
+    const uint4 z4 = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < nx * PIECES; i += DT) {
+        const int r = i / PIECES, pc = i - r * PIECES;
+        const bool in = d0 + pc * 8 < D && xt0 + r >= 0;
+        reinterpret_cast<uint4*>(xs)[i] = in ? *reinterpret_cast<const uint4*>(xb + static_cast<long long>(xt0 + r) * p.ld_x + pc * 8) : z4;
+    }
+    for (int i = tid; i < ng * PIECES; i += DT) {
+        const int r = i / PIECES, pc = i - r * PIECES;
+        const bool in = d0 + pc * 8 < D;
+        reinterpret_cast<uint4*>(gs)[i] = in ? *reinterpret_cast<const uint4*>(gb + static_cast<long long>(t0 + r) * p.ld_du + pc * 8) : z4;
+    }
+    const int d = d0 + tid;
+    const bool d_ok = d < D;
+    const bool has_neg = t0 < K;  // only the first chunk reaches the entering window
+    if (has_neg) {
+        for (int k = 0; k < K; ++k)
+            xneg[k * DT + tid] = (p.state_in && d_ok) ? p.state_in[(static_cast<long long>(b) * D + d) * K + k] : 0.0f;
+    }
+    __syncthreads();
+    // x[t] for t in [-K, T)
+    auto xat = [&](int t) { return (has_neg && t < 0) ? xneg[(K + t) * DT + tid] : to_f(xs[(t - xt0) * DT + tid]); };
+    float w[KV], win[KV], dco[KV - 1], dW[KV], bias = 0.0f, db = 0.0f;
+#pragma unroll
+    for (int k = 0; k < KV; ++k) {
+        const int kk = k - (KV - K);
+        w[k] = (kk >= 0 && d_ok) ? p.w[static_cast<long long>(d) * K + kk] : 0.0f;
+        win[k] = kk >= 0 ? xat(t_start - (KV - 1) + k) : 0.0f;
+        dW[k] = 0.0f;
+        if (k < KV - 1) dco[k] = 0.0f;
+    }
+    if (d_ok) bias = p.bias[d];
+    // One step back in time: gv = d_u[t], xin = x[t - K] (enters the window), OUT: t < t1.
+    auto step = [&](auto out_tag, float gv, float xin, Tact* dst) {
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) acc = fmaf(win[k], w[k], acc);
+        const float sg = sigmoidf_fast(acc);
+        const float g = gv * sg * fmaf(acc, 1.0f - sg, 1.0f);
+        if (decltype(out_tag)::value) {
+            db += g;
+            float dx = g * w[KV - 1];
+#pragma unroll
+            for (int k = 0; k < KV; ++k) dW[k] = fmaf(g, win[k], dW[k]);
+            // future steps: dco[j] = dco[t + 1 + j] meets tap KV-2-j
+#pragma unroll
+            for (int j = 0; j < KV - 1; ++j) dx = fmaf(dco[j], w[KV - 2 - j], dx);
+            *dst = from_f<Tact>(dx);
+        }
+#pragma unroll
+        for (int j = KV - 2; j > 0; --j) dco[j] = dco[j - 1];
+        dco[0] = g;
+#pragma unroll
+        for (int k = KV - 1; k > 0; --k) win[k] = win[k - 1];
+        // x[t - K] enters at the oldest tap that exists (slot KV - K)
+#pragma unroll
+        for (int k = 0; k < KV; ++k)
+            if (k == KV - K) win[k] = xin;
+    };
+    // the halo steps after the chunk feed dco only
+    for (int t = t_start; t >= t1; --t) step(std::false_type{}, to_f(gs[(t - t0) * DT + tid]), xat(t - K), dxs);
+    const int n = t1 - t0;
+    const Tact* gp = gs + (n - 1) * DT + tid;
+    Tact* dp = dxs + (n - 1) * DT + tid;
+    if (has_neg) {
+        for (int i = n - 1; i >= 0; --i, gp -= DT, dp -= DT) step(std::true_type{}, to_f(*gp), xat(t0 + i - K), dp);
+    } else {
+        const Tact* xp = xs + (n - 1) * DT + tid;  // x[t - K] sits K rows below x[t]: row (t - K) - xt0 = t - t0
+        int i = n;
+        for (; i >= 8; i -= 8) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) step(std::true_type{}, to_f(gp[-u * DT]), to_f(xp[-u * DT]), dp - u * DT);
+            gp -= 8 * DT; xp -= 8 * DT; dp -= 8 * DT;
+        }
+        for (; i > 0; --i, gp -= DT, xp -= DT, dp -= DT) step(std::true_type{}, to_f(*gp), to_f(*xp), dp);
+    }
+    if (d_ok) {
+        float* pt = p.part + ((static_cast<long long>(b) * gridDim.y + chunk) * D + d) * (K + 1);
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int kk = k - (KV - K);
+            if (kk >= 0) pt[kk] = dW[k];
+        }
+        pt[K] = db;
+    }
+    __syncthreads();
+    for (int i = tid; i < (t1 - t0) * PIECES; i += DT) {
+        const int r = i / PIECES, pc = i - r * PIECES;
+        if (d0 + pc * 8 < D)
+            *reinterpret_cast<uint4*>(dxb + static_cast<long long>(t0 + r) * p.ld_dx + pc * 8) = reinterpret_cast<const uint4*>(dxs)[i];
+    }
+}
+
+int conv_configure(Ctx* c) {
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(conv1d_bwd_tile_kernel<__half>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, conv_tile_smem<__half>()));
+    MB200_CUDA_CHECK(c, cudaFuncSetAttribute(reinterpret_cast<const void*>(conv1d_bwd_tile_kernel<__nv_bfloat16>),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             conv_tile_smem<__nv_bfloat16>()));
+    return MAMBA_B200_OK;
+}
+
 // The vector kernels need d_conv <= 4 and every row start on a vector boundary.
 static bool conv_vec_ok(int K, int D, int vec, size_t esize, std::initializer_list<const void*> ptrs,
                         std::initializer_list<long long> lds) {
@@ -643,7 +779,15 @@ extern "C" MAMBA_B200_API int mamba_b200_conv1d_bwd(void* handle, void* stream,
     const bool use_vec = conv_vec_ok(a.K, a.D, bvec, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx}) &&
                          reinterpret_cast<uintptr_t>(a.conv_w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.conv_b) % 16 == 0;
     dim3 vgrid((a.D / bvec + 63) / 64, chunks, a.B);
-    if (a.dtype == MAMBA_B200_F32) {
+    // 16-bit storage with rows on 16-byte boundaries: the shared-memory tile kernel
+    const bool use_tile = es == 2 && conv_vec_ok(a.K, a.D, 8, es, {a.x, a.d_u, a.d_x}, {a.ld_x, a.ld_du, a.ld_dx});
+    if (use_tile) {
+        dim3 tgrid((a.D + kConvTileD - 1) / kConvTileD, chunks, a.B);
+        if (a.dtype == MAMBA_B200_F16)
+            conv1d_bwd_tile_kernel<__half><<<tgrid, kConvTileD, conv_tile_smem<__half>(), st>>>(p);
+        else
+            conv1d_bwd_tile_kernel<__nv_bfloat16><<<tgrid, kConvTileD, conv_tile_smem<__nv_bfloat16>(), st>>>(p);
+    } else if (a.dtype == MAMBA_B200_F32) {
         if (use_vec) conv1d_bwd_vec_kernel<float><<<vgrid, 64, 0, st>>>(p);
         else conv1d_bwd_kernel<float><<<grid, 128, 0, st>>>(p);
     } else if (a.dtype == MAMBA_B200_F16) {
