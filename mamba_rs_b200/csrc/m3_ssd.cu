@@ -691,19 +691,21 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_fwd(void* handle, void* stream,
     p.status = c->d_status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    const bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd <= tc::HD && a.hd % 8 == 0 && a.N <= tc::NS &&
-                             a.N % 8 == 0 && !a.carry_in &&
-                             !a.force_sequential && al16(a.x) && al16(a.y) &&
-                             (gen ? al16(a.Bn) && al16(a.Cn) && al16(a.angle_vel) : al16(a.K) && al16(a.Q));
+    bool tensor_core = a.dtype != MAMBA_B200_F32 && a.hd <= tc::HD && a.hd % 8 == 0 && a.N <= tc::NS &&
+                       a.N % 8 == 0 && !a.carry_in &&
+                       !a.force_sequential && al16(a.x) && al16(a.y) &&
+                       (gen ? al16(a.Bn) && al16(a.Cn) && al16(a.angle_vel) : al16(a.K) && al16(a.Q));
+    // the tile maps; when the driver refuses one (no encoder, a stride beyond its range) the
+    // sequential kernel takes the call
+    tensor_core = tensor_core &&
+                  make_tmap_head_tile(c, &p.tm_q, a.dtype, gen ? a.Cn : a.Q, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
+                  make_tmap_head_tile(c, &p.tm_k, a.dtype, gen ? a.Bn : a.K, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
+                  make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B);
     if (gen && !tensor_core)
         return fail(c, MAMBA_B200_ERR_SHAPE, "m3_ssd_fwd: K/Q generation runs on the tensor-core path only (16-bit "
                                               "storage, headdim <= 64, d_state <= 128, multiples of 8, no carried "
                                               "state, 16-byte aligned tensors)");
     if (tensor_core) {
-        const bool maps = make_tmap_head_tile(c, &p.tm_q, a.dtype, gen ? a.Cn : a.Q, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
-                          make_tmap_head_tile(c, &p.tm_k, a.dtype, gen ? a.Bn : a.K, a.N, gen ? a.ng : a.nh, a.T, a.B) &&
-                          make_tmap_head_tile(c, &p.tm_v, a.dtype, a.x, a.hd, a.nh, a.T, a.B);
-        if (!maps) return fail(c, MAMBA_B200_ERR_CUDA, "m3_ssd_fwd: tensor map encoding failed");
         p.wide_y = a.hd % 16 == 0 && reinterpret_cast<uintptr_t>(a.y) % 32 == 0;
         p.sc_tma = a.nh % 4 == 0 &&
                    make_tmap_3d(c, &p.tm_adt, MAMBA_B200_F32, a.adt, a.nh, a.nh, a.T, a.B, 4, 129) &&
