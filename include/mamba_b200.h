@@ -408,7 +408,7 @@ MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream, const mamba
  * This entry point has no counterpart in the reference.
  *
  * It is meant for an engine that must not create device memory on this path:
- * one that handed its whole budget to an arena sized before this kernel's
+ * one that handed all of its memory to an arena sized before this kernel's
  * scratch was known, or one that runs beside latency-critical streams, which a
  * cudaMalloc would stall because it synchronises the device (and which can
  * simply fail when another allocator owns the remaining memory).  The call
