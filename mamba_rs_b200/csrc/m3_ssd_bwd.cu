@@ -470,16 +470,15 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
     };
 
     // Cooperative asynchronous load of a [128 x C] tile of 16-bit rows (row stride `ld`
-    // elements) into the core-matrix layout; rows >= nv are zero-filled.
+    // elements) into the 128-byte-swizzled layout (m3_tc.cuh); rows >= nv are zero-filled.
     const int r8 = threadIdx.x & 7, jc = (threadIdx.x & 31) >> 3, wfull = threadIdx.x >> 5;
     auto issue_rows = [&](const Th* base, long long ld, uint32_t tile, int C, int cols, int nv) {
         const int jgroups = C / 32;  // groups of four 16-byte pieces per row
-        const uint32_t dst0 = tile + r8 * 16 + jc * 128;
         for (int task = wfull; task < 16 * jgroups; task += 8) {
             const int rg = task / jgroups, jg = task - rg * jgroups, row = rg * 8 + r8;
             const int col = 8 * jc + 32 * jg;
             const bool ok = row < nv && col < cols;
-            cp_async16(smem + dst0 + rg * (C / 8) * 128 + jg * 512,
+            cp_async16(smem + tile + sw_chunk(row, jc + 4 * jg),
                        base + static_cast<long long>(min(row, nv - 1)) * ld + (ok ? col : 0), ok);
         }
     };
@@ -501,14 +500,14 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             __syncthreads();
 #pragma unroll
             for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(smem + kV + chunk_off(tid, j, HD));
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + kV + sw_chunk(tid, j));
                 uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const float2 f = unpack2<Th>(w4[q4]);
                     w4[q4] = pack2<Th>(f.x * wt, f.y * wt);
                 }
-                *reinterpret_cast<uint4*>(smem + kDY + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                *reinterpret_cast<uint4*>(smem + kDY + sw_chunk(tid, j)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
         }
         if (c > 0) {  // state entering chunk c: copy out, then decay for the update
@@ -519,7 +518,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 tmem_ld32(lane_addr + cDS + q2 * 32, sv);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(ws_st + static_cast<size_t>(c) * kStateTile + chunk_off(tid, q2 * 4 + j, HD)) =
+                    *reinterpret_cast<uint4*>(ws_st + static_cast<size_t>(c) * kStateTile + sw_chunk(tid, q2 * 4 + j)) =
                         make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
                                    pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
                 if (!last) {
@@ -538,7 +537,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             const uint32_t idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // S^T[n][p] += sum_t K[t][n] (w V)[t][p]
-                mma(tmem + cDS, desc_mnmajor(sbase + kK, k, NS), desc_mnmajor(sbase + kDY, k, HD), idS, c > 0 || k > 0);
+                mma(tmem + cDS, desc_sw_mn(sbase + kK, k), desc_sw_mn(sbase + kDY, k), idS, c > 0 || k > 0);
             commit(&bars[3]);
         }
         wait_bar(3);
@@ -581,14 +580,14 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         // E o dY from the landed dY tile (own row, own half of the columns)
 #pragma unroll
         for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-            const uint4 dyv = *reinterpret_cast<const uint4*>(smem + kDY + chunk_off(tid, j, HD));
+            const uint4 dyv = *reinterpret_cast<const uint4*>(smem + kDY + sw_chunk(tid, j));
             uint32_t w4[4] = {dyv.x, dyv.y, dyv.z, dyv.w};
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
                 const float2 f = unpack2<Th>(w4[q4]);
                 w4[q4] = pack2<Th>(f.x * e_t, f.y * e_t);
             }
-            *reinterpret_cast<uint4*>(smem + kEdY + chunk_off(tid, j, HD)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            *reinterpret_cast<uint4*>(smem + kEdY + sw_chunk(tid, j)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
         fence_proxy_async();
         fence_before();
@@ -599,19 +598,19 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idW = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
             for (int k = 0; k < NS / 16; ++k)  // G[t][s] = sum_n Q[t][n] K[s][n]
-                mma(tmem + c0, desc_kmajor(sbase + kQ, k, NS), desc_kmajor(sbase + kK, k, NS), idKK, k > 0);
+                mma(tmem + c0, desc_sw_k(sbase + kQ, k), desc_sw_k(sbase + kK, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)  // P[t][s] = sum_p dY[t][p] V[s][p]
-                mma(tmem + c1, desc_kmajor(sbase + kDY, k, HD), desc_kmajor(sbase + kV, k, HD), idKK, k > 0);
+                mma(tmem + c1, desc_sw_k(sbase + kDY, k), desc_sw_k(sbase + kV, k), idKK, k > 0);
             if (has_sin) {
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)  // R'[t][n] = sum_p (E dY)[t][p] S_in^T[n][p]
-                    mma(tmem + c2, desc_kmajor(sbase + kEdY, k, HD), desc_kmajor(sbase + kSin, k, HD), idKK, k > 0);
+                    mma(tmem + c2, desc_sw_k(sbase + kEdY, k), desc_sw_k(sbase + kSin, k), idKK, k > 0);
             }
             if (has_ds) {
 #pragma unroll
                 for (int k = 0; k < NS / 16; ++k)  // W[s][p] = sum_n K[s][n] dS^T[n][p]
-                    mma(tmem + c3, desc_kmajor(sbase + kK, k, NS), desc_mnmajor(sbase + kDS, k, HD), idW, k > 0);
+                    mma(tmem + c3, desc_sw_k(sbase + kK, k), desc_sw_mn(sbase + kDS, k), idW, k > 0);
             }
             commit(&bars[0]);
         }
@@ -655,9 +654,9 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) =
+                *reinterpret_cast<uint4*>(smem + kM1 + sw_chunk(tid, q4 * 4 + j)) =
                     make_uint4(pk1[4 * j], pk1[4 * j + 1], pk1[4 * j + 2], pk1[4 * j + 3]);
-                *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) =
+                *reinterpret_cast<uint4*>(smem + kM2 + sw_chunk(tid, q4 * 4 + j)) =
                     make_uint4(pk2[4 * j], pk2[4 * j + 1], pk2[4 * j + 2], pk2[4 * j + 3]);
             }
         };
@@ -665,8 +664,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             if (q4 > warp) {  // wholly above the diagonal for every row of this warp
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    *reinterpret_cast<uint4*>(smem + kM1 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
-                    *reinterpret_cast<uint4*>(smem + kM2 + chunk_off(tid, q4 * 4 + j, CS)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + kM1 + sw_chunk(tid, q4 * 4 + j)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + kM2 + sw_chunk(tid, q4 * 4 + j)) = zero4;
                 }
             } else if (q4 == warp) {
                 mask_block(std::true_type{}, q4);
@@ -684,7 +683,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 tmem_ld32(lane_addr + c2 + q4 * 32, rv);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + chunk_off(tid, q4 * 4 + j, NS));
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + sw_chunk(tid, q4 * 4 + j));
                     const uint32_t w4[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -707,7 +706,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 if (has_sin) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 sv = *reinterpret_cast<const uint4*>(smem + kSin + chunk_off(tid, q2 * 4 + j, HD));
+                        const uint4 sv = *reinterpret_cast<const uint4*>(smem + kSin + sw_chunk(tid, q2 * 4 + j));
                         const uint32_t w4[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
@@ -732,16 +731,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                            idV = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < NS / 16; ++k)  // G^T[s][t]
-                mma(tmem + c0, desc_kmajor(sbase + kK, k, NS), desc_kmajor(sbase + kQ, k, NS), idKK, k > 0);
+                mma(tmem + c0, desc_sw_k(sbase + kK, k), desc_sw_k(sbase + kQ, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)  // P^T[s][t]
-                mma(tmem + c1, desc_kmajor(sbase + kV, k, HD), desc_kmajor(sbase + kDY, k, HD), idKK, k > 0);
+                mma(tmem + c1, desc_sw_k(sbase + kV, k), desc_sw_k(sbase + kDY, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dQ[t][n] (+)= sum_s M1[t][s] K[s][n]
-                mma(tmem + c2, desc_kmajor(sbase + kM1, k, CS), desc_mnmajor(sbase + kK, k, NS), idQ, has_sin || k > 0);
+                mma(tmem + c2, desc_sw_k(sbase + kM1, k), desc_sw_mn(sbase + kK, k), idQ, has_sin || k > 0);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dV[s][p] (+)= sum_t M2[t][s] dY[t][p]
-                mma(tmem + c3, desc_mnmajor(sbase + kM2, k, CS), desc_mnmajor(sbase + kDY, k, HD), idV, has_ds || k > 0);
+                mma(tmem + c3, desc_sw_mn(sbase + kM2, k), desc_sw_mn(sbase + kDY, k), idV, has_ds || k > 0);
             commit(&bars[1]);
         }
         wait_bar(1);
@@ -777,7 +776,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + chunk_off(tid, q4 * 4 + j, NS));
+                        const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + sw_chunk(tid, q4 * 4 + j));
                         const uint32_t w4[4] = {kv.x, kv.y, kv.z, kv.w};
                         float o[8];
 #pragma unroll
@@ -799,7 +798,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                     uint4 ox[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 yv = *reinterpret_cast<const uint4*>(smem + kDY + chunk_off(tid, q2 * 4 + j, HD));
+                        const uint4 yv = *reinterpret_cast<const uint4*>(smem + kDY + sw_chunk(tid, q2 * 4 + j));
                         const uint32_t w4[4] = {yv.x, yv.y, yv.z, yv.w};
                         uint32_t o[4];
 #pragma unroll
@@ -830,15 +829,15 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                            idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dK[s][n] = sum_t M1[t][s] Q[t][n]
-                mma(tmem + c0, desc_mnmajor(sbase + kM1, k, CS), desc_mnmajor(sbase + kQ, k, NS), idK, k > 0);
+                mma(tmem + c0, desc_sw_mn(sbase + kM1, k), desc_sw_mn(sbase + kQ, k), idK, k > 0);
             if (has_ds) {
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)  // U[s][n] = sum_p V[s][p] dS^T[n][p]
-                    mma(tmem + c1, desc_kmajor(sbase + kV, k, HD), desc_kmajor(sbase + kDS, k, HD), idU, k > 0);
+                    mma(tmem + c1, desc_sw_k(sbase + kV, k), desc_sw_k(sbase + kDS, k), idU, k > 0);
             }
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dS^T[n][p] (+)= sum_t Q[t][n] (E dY)[t][p]
-                mma(tmem + cDS, desc_mnmajor(sbase + kQ, k, NS), desc_mnmajor(sbase + kEdY, k, HD), idS, has_ds || k > 0);
+                mma(tmem + cDS, desc_sw_mn(sbase + kQ, k), desc_sw_mn(sbase + kEdY, k), idS, has_ds || k > 0);
             commit(&bars[2]);
         }
         wait_bar(2);
@@ -851,7 +850,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 tmem_ld32(lane_addr + cDS + q2 * 32, sv);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(smem + kDS + chunk_off(tid, q2 * 4 + j, HD)) =
+                    *reinterpret_cast<uint4*>(smem + kDS + sw_chunk(tid, q2 * 4 + j)) =
                         make_uint4(pack2<Th>(sv[8 * j], sv[8 * j + 1]), pack2<Th>(sv[8 * j + 2], sv[8 * j + 3]),
                                    pack2<Th>(sv[8 * j + 4], sv[8 * j + 5]), pack2<Th>(sv[8 * j + 6], sv[8 * j + 7]));
             }
@@ -869,8 +868,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 else tmem_ld32(lane_addr + c0 + q4 * 32, av);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + chunk_off(tid, q4 * 4 + j, NS));
-                    const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + chunk_off(tid, q4 * 4 + j, NS));
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + sw_chunk(tid, q4 * 4 + j));
+                    const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + sw_chunk(tid, q4 * 4 + j));
                     const uint32_t q4w[4] = {qv.x, qv.y, qv.z, qv.w};
                     const uint32_t k4w[4] = {kv.x, kv.y, kv.z, kv.w};
                     float o[8];
