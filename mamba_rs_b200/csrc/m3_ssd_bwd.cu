@@ -34,6 +34,8 @@ struct M3BwdParams {
     // tensor-core kernel: adt, dt, trap [B,T,nh] f32 as boxes of 4 heads x 129 rows (valid when
     // sc_tma; needs nheads % 4 == 0)
     CUtensorMap tm_adt, tm_dt, tm_trap;
+    // tensor-core kernel: Q, K, x, dy as [128 x 64] swizzled sub-tile maps
+    CUtensorMap tm_q, tm_k, tm_x, tm_dy;
     int sc_tma;
     int wide_st;  // dK and dQ are 32-byte aligned: their rows leave as 256-bit stores
     int wide_dx;  // the same for dx (headdim a multiple of 16)
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
     const uint32_t sbase = smem_u32(smem);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);  // 5: the chunk's tiles have landed (TMA)
         fence_barrier_init();
     }
     if (threadIdx.x < 32) {
@@ -469,18 +471,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         return red[0] + red[1] + red[2] + red[3];
     };
 
-    // Cooperative asynchronous load of a [128 x C] tile of 16-bit rows (row stride `ld`
-    // elements) into the 128-byte-swizzled layout (m3_tc.cuh); rows >= nv are zero-filled.
-    const int r8 = threadIdx.x & 7, jc = (threadIdx.x & 31) >> 3, wfull = threadIdx.x >> 5;
-    auto issue_rows = [&](const Th* base, long long ld, uint32_t tile, int C, int cols, int nv) {
-        const int jgroups = C / 32;  // groups of four 16-byte pieces per row
-        for (int task = wfull; task < 16 * jgroups; task += 8) {
-            const int rg = task / jgroups, jg = task - rg * jgroups, row = rg * 8 + r8;
-            const int col = 8 * jc + 32 * jg;
-            const bool ok = row < nv && col < cols;
-            cp_async16(smem + tile + sw_chunk(row, jc + 4 * jg),
-                       base + static_cast<long long>(min(row, nv - 1)) * ld + (ok ? col : 0), ok);
-        }
+    // Tiles come by TMA (one thread; rows past T and columns past the head's width arrive as
+    // zeros), the 16-bit state copy of a chunk by one contiguous bulk copy.
+    uint32_t tfph = 0;
+    auto load_qk = [&](uint32_t tile, const CUtensorMap* map, int t0) {
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) tma_load_4d(smem + tile + sub * kSwSub, map, &bars[5], 64 * sub, h, t0, b);
+    };
+    auto wait_tiles = [&]() {
+        ok = mbar_wait(&bars[5], tfph, p.status) && ok;
+        tfph ^= 1;
     };
 
     // ---------------- A. forward: 16-bit copies of the entering states ----------------
@@ -490,14 +490,15 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         float run = 0.0f, g = 0.0f, s = 0.0f;
         if (!last) {
             issue_scalars(t0);
-            issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
-            issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
-            cp_async_commit();
+            if (threadIdx.x == 0) {
+                mbar_expect_tx(&bars[5], 2 * kSwSub + kSwSub);
+                load_qk(kK, &p.tm_k, t0);
+                tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
+            }
             load_scalars(t0, nv, run, g, s);
             const float dA_end = dA[nv - 1];
             const float wt = tid < nv ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
-            cp_async_wait_all();
-            __syncthreads();
+            wait_tiles();
 #pragma unroll
             for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
                 const uint4 v = *reinterpret_cast<const uint4*>(smem + kV + sw_chunk(tid, j));
@@ -542,8 +543,10 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         }
         wait_bar(3);
     }
+    // the state copies of this CTA (generic stores) are read back below by bulk copies
+    asm volatile("fence.proxy.async;" ::: "memory");
     fence_before();
-    __syncthreads();  // state copies of this CTA are in global memory (read back below by the same CTA)
+    __syncthreads();
     fence_after();
 
     // ---------------- B. backward over the chunks ----------------
@@ -554,19 +557,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         const int t = t0 + tid;
         const bool row_ok = tid < nv;
         const bool has_sin = c > 0;
-        // ---- loads (asynchronous, 8 rows x 64 bytes per warp instruction) under the scalars ----
+        // ---- this chunk's tiles ----
         issue_scalars(t0);
-        issue_rows(Qg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kQ, NS, nsv, nv);
-        issue_rows(Kg + ((static_cast<long long>(b) * T + t0) * nh + h) * nsv, static_cast<long long>(nh) * nsv, kK, NS, nsv, nv);
-        issue_rows(xg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kV, HD, hdv, nv);
-        issue_rows(dyg + (static_cast<long long>(b) * T + t0) * nh * hdv + h * hdv, static_cast<long long>(nh) * hdv, kDY, HD, hdv, nv);
-        if (has_sin) {
-            const uint4* src = reinterpret_cast<const uint4*>(ws_st + static_cast<size_t>(c) * kStateTile);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                cp_async16(smem + kSin + (j * 256 + threadIdx.x) * 16, src + j * 256 + threadIdx.x, true);
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(&bars[5], 4 * kSwSub + 2 * kSwSub + (has_sin ? kStateTile : 0));
+            load_qk(kQ, &p.tm_q, t0);
+            load_qk(kK, &p.tm_k, t0);
+            tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
+            tma_load_4d(smem + kDY, &p.tm_dy, &bars[5], 0, h, t0, b);
+            if (has_sin) bulk_load(smem + kSin, ws_st + static_cast<size_t>(c) * kStateTile, kStateTile, &bars[5]);
         }
-        cp_async_commit();
         float run, g_t, s_t;
         load_scalars(t0, nv, run, g_t, s_t);
         const float dA_t = run, dA_end = dA[nv - 1];
@@ -575,8 +575,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         const float w_t = lend_t * s_t;
         const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * nsv;
         const long long x_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
-        cp_async_wait_all();
-        __syncthreads();
+        wait_tiles();
         // E o dY from the landed dY tile (own row, own half of the columns)
 #pragma unroll
         for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
@@ -1015,8 +1014,16 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
         !a.d_adt || !a.d_dt || !a.d_trap || !a.dD || !a.workspace)
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: null required pointer");
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    M3BwdParams p;
+    memset(&p, 0, sizeof(p));
+    // the tensor-core kernel needs its four tile maps; without them (no encoder, a stride beyond
+    // its range) the CUDA-core kernel takes the call
     const bool tensor_core = m3_bwd_tc_shape(a.dtype, a.hd, a.N) && al16(a.x) && al16(a.K) &&
-                             al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) && al16(a.dQ);
+                             al16(a.Q) && al16(a.dy) && al16(a.dx) && al16(a.dK) && al16(a.dQ) &&
+                             make_tmap_head_tile(c, &p.tm_q, a.dtype, a.Q, a.N, a.nh, a.T, a.B) &&
+                             make_tmap_head_tile(c, &p.tm_k, a.dtype, a.K, a.N, a.nh, a.T, a.B) &&
+                             make_tmap_head_tile(c, &p.tm_x, a.dtype, a.x, a.hd, a.nh, a.T, a.B) &&
+                             make_tmap_head_tile(c, &p.tm_dy, a.dtype, a.dy, a.hd, a.nh, a.T, a.B);
     size_t o_g, o_s, o_d, total;
     // a misaligned tensor-core-shaped call falls back to the CUDA-core kernel and its larger scratch
     m3_bwd_ws(tensor_core, a.B, a.T, a.nh, a.hd, a.N, &o_g, &o_s, &o_d, &total);
@@ -1024,8 +1031,6 @@ extern "C" MAMBA_B200_API int mamba_b200_m3_ssd_bwd(void* handle, void* stream,
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: workspace %lld < %zu bytes", a.workspace_bytes, total);
     if (reinterpret_cast<uintptr_t>(a.workspace) % 256)
         return fail(c, MAMBA_B200_ERR_ARG, "m3_ssd_bwd: workspace must be 256-byte aligned");
-    M3BwdParams p;
-    memset(&p, 0, sizeof(p));
     p.x = a.x; p.K = a.K; p.Q = a.Q; p.dy = a.dy; p.dt = a.dt; p.trap = a.trap; p.adt = a.adt; p.Dh = a.Dh;
     p.dx = a.dx; p.dK = a.dK; p.dQ = a.dQ; p.d_adt = a.d_adt; p.d_dt = a.d_dt; p.d_trap = a.d_trap; p.dD = a.dD;
     unsigned char* ws = static_cast<unsigned char*>(a.workspace);
