@@ -410,13 +410,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
     // loads with their latency exposed; without the maps (nheads % 4 != 0) the loads remain.
     uint32_t scph = 0;
     const int hcol = h & 3;
-    auto issue_scalars = [&](int t0) {
-        if (p.sc_tma && threadIdx.x == 0) {
+    auto issue_scalars_now = [&](int t0) {  // one thread
+        if (p.sc_tma) {
             mbar_expect_tx(&bars[4], 3 * 129 * 16);
             tma_load_3d(smem + kStage, &p.tm_adt, &bars[4], h & ~3, t0, b);
             tma_load_3d(smem + kStage + kStageArr, &p.tm_dt, &bars[4], h & ~3, t0, b);
             tma_load_3d(smem + kStage + 2 * kStageArr, &p.tm_trap, &bars[4], h & ~3, t0, b);
         }
+    };
+    auto issue_scalars = [&](int t0) {
+        if (threadIdx.x == 0) issue_scalars_now(t0);
     };
     // per-row scalars of chunk c -> dA (inclusive cumsum), scl, gam in shared memory
     auto load_scalars = [&](int t0, int nv, float& run_o, float& g_o, float& s_o) {
@@ -552,21 +555,28 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
     // ---------------- B. backward over the chunks ----------------
     bool has_ds = false;
     float dD_acc = 0.0f;
-    for (int c = nc - 1; c >= 0; --c) {
+    // The tiles of a chunk are requested while the previous chunk's last epilogue runs: as soon
+    // as its last MMA group is done, Q and K of the next chunk go where this chunk's M1 and M2
+    // were (the two pairs of tiles swap places every chunk, so nothing is double-buffered), V, dY
+    // and the entering state go to their own tiles.
+    auto request_tiles = [&](int c, uint32_t q_tile, uint32_t k_tile) {  // one thread
+        const int t0 = c * CS;
+        issue_scalars_now(t0);
+        mbar_expect_tx(&bars[5], 4 * kSwSub + 2 * kSwSub + (c > 0 ? kStateTile : 0));
+        load_qk(q_tile, &p.tm_q, t0);
+        load_qk(k_tile, &p.tm_k, t0);
+        tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
+        tma_load_4d(smem + kDY, &p.tm_dy, &bars[5], 0, h, t0, b);
+        if (c > 0) bulk_load(smem + kSin, ws_st + static_cast<size_t>(c) * kStateTile, kStateTile, &bars[5]);
+    };
+    if (threadIdx.x == 0 && nc > 0) request_tiles(nc - 1, kQ, kK);
+    for (int c = nc - 1, it = 0; c >= 0; --c, ++it) {
+        const bool par = (it & 1) != 0;
+        const uint32_t tQ = par ? kM1 : kQ, tK = par ? kM2 : kK, tM1 = par ? kQ : kM1, tM2 = par ? kK : kM2;
         const int t0 = c * CS, nv = min(CS, T - t0);
         const int t = t0 + tid;
         const bool row_ok = tid < nv;
         const bool has_sin = c > 0;
-        // ---- this chunk's tiles ----
-        issue_scalars(t0);
-        if (threadIdx.x == 0) {
-            mbar_expect_tx(&bars[5], 4 * kSwSub + 2 * kSwSub + (has_sin ? kStateTile : 0));
-            load_qk(kQ, &p.tm_q, t0);
-            load_qk(kK, &p.tm_k, t0);
-            tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
-            tma_load_4d(smem + kDY, &p.tm_dy, &bars[5], 0, h, t0, b);
-            if (has_sin) bulk_load(smem + kSin, ws_st + static_cast<size_t>(c) * kStateTile, kStateTile, &bars[5]);
-        }
         float run, g_t, s_t;
         load_scalars(t0, nv, run, g_t, s_t);
         const float dA_t = run, dA_end = dA[nv - 1];
@@ -597,7 +607,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             const uint32_t idKK = instr_desc(fmt, 0, 0, 128), idW = instr_desc(fmt, 0, 1, 64);
 #pragma unroll
             for (int k = 0; k < NS / 16; ++k)  // G[t][s] = sum_n Q[t][n] K[s][n]
-                mma(tmem + c0, desc_sw_k(sbase + kQ, k), desc_sw_k(sbase + kK, k), idKK, k > 0);
+                mma(tmem + c0, desc_sw_k(sbase + tQ, k), desc_sw_k(sbase + tK, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)  // P[t][s] = sum_p dY[t][p] V[s][p]
                 mma(tmem + c1, desc_sw_k(sbase + kDY, k), desc_sw_k(sbase + kV, k), idKK, k > 0);
@@ -609,7 +619,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             if (has_ds) {
 #pragma unroll
                 for (int k = 0; k < NS / 16; ++k)  // W[s][p] = sum_n K[s][n] dS^T[n][p]
-                    mma(tmem + c3, desc_sw_k(sbase + kK, k), desc_sw_mn(sbase + kDS, k), idW, k > 0);
+                    mma(tmem + c3, desc_sw_k(sbase + tK, k), desc_sw_mn(sbase + kDS, k), idW, k > 0);
             }
             commit(&bars[0]);
         }
@@ -653,9 +663,9 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                *reinterpret_cast<uint4*>(smem + kM1 + sw_chunk(tid, q4 * 4 + j)) =
+                *reinterpret_cast<uint4*>(smem + tM1 + sw_chunk(tid, q4 * 4 + j)) =
                     make_uint4(pk1[4 * j], pk1[4 * j + 1], pk1[4 * j + 2], pk1[4 * j + 3]);
-                *reinterpret_cast<uint4*>(smem + kM2 + sw_chunk(tid, q4 * 4 + j)) =
+                *reinterpret_cast<uint4*>(smem + tM2 + sw_chunk(tid, q4 * 4 + j)) =
                     make_uint4(pk2[4 * j], pk2[4 * j + 1], pk2[4 * j + 2], pk2[4 * j + 3]);
             }
         };
@@ -663,8 +673,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             if (q4 > warp) {  // wholly above the diagonal for every row of this warp
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    *reinterpret_cast<uint4*>(smem + kM1 + sw_chunk(tid, q4 * 4 + j)) = zero4;
-                    *reinterpret_cast<uint4*>(smem + kM2 + sw_chunk(tid, q4 * 4 + j)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + tM1 + sw_chunk(tid, q4 * 4 + j)) = zero4;
+                    *reinterpret_cast<uint4*>(smem + tM2 + sw_chunk(tid, q4 * 4 + j)) = zero4;
                 }
             } else if (q4 == warp) {
                 mask_block(std::true_type{}, q4);
@@ -682,7 +692,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 tmem_ld32(lane_addr + c2 + q4 * 32, rv);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + sw_chunk(tid, q4 * 4 + j));
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + tQ + sw_chunk(tid, q4 * 4 + j));
                     const uint32_t w4[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -730,16 +740,16 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                            idV = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < NS / 16; ++k)  // G^T[s][t]
-                mma(tmem + c0, desc_sw_k(sbase + kK, k), desc_sw_k(sbase + kQ, k), idKK, k > 0);
+                mma(tmem + c0, desc_sw_k(sbase + tK, k), desc_sw_k(sbase + tQ, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)  // P^T[s][t]
                 mma(tmem + c1, desc_sw_k(sbase + kV, k), desc_sw_k(sbase + kDY, k), idKK, k > 0);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dQ[t][n] (+)= sum_s M1[t][s] K[s][n]
-                mma(tmem + c2, desc_sw_k(sbase + kM1, k), desc_sw_mn(sbase + kK, k), idQ, has_sin || k > 0);
+                mma(tmem + c2, desc_sw_k(sbase + tM1, k), desc_sw_mn(sbase + tK, k), idQ, has_sin || k > 0);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dV[s][p] (+)= sum_t M2[t][s] dY[t][p]
-                mma(tmem + c3, desc_sw_mn(sbase + kM2, k), desc_sw_mn(sbase + kDY, k), idV, has_ds || k > 0);
+                mma(tmem + c3, desc_sw_mn(sbase + tM2, k), desc_sw_mn(sbase + kDY, k), idV, has_ds || k > 0);
             commit(&bars[1]);
         }
         wait_bar(1);
@@ -775,7 +785,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + sw_chunk(tid, q4 * 4 + j));
+                        const uint4 kv = *reinterpret_cast<const uint4*>(smem + tK + sw_chunk(tid, q4 * 4 + j));
                         const uint32_t w4[4] = {kv.x, kv.y, kv.z, kv.w};
                         float o[8];
 #pragma unroll
@@ -828,7 +838,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                            idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dK[s][n] = sum_t M1[t][s] Q[t][n]
-                mma(tmem + c0, desc_sw_mn(sbase + kM1, k), desc_sw_mn(sbase + kQ, k), idK, k > 0);
+                mma(tmem + c0, desc_sw_mn(sbase + tM1, k), desc_sw_mn(sbase + tQ, k), idK, k > 0);
             if (has_ds) {
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)  // U[s][n] = sum_p V[s][p] dS^T[n][p]
@@ -836,10 +846,11 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             }
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // dS^T[n][p] (+)= sum_t Q[t][n] (E dY)[t][p]
-                mma(tmem + cDS, desc_sw_mn(sbase + kQ, k), desc_sw_mn(sbase + kEdY, k), idS, has_ds || k > 0);
+                mma(tmem + cDS, desc_sw_mn(sbase + tQ, k), desc_sw_mn(sbase + kEdY, k), idS, has_ds || k > 0);
             commit(&bars[2]);
         }
         wait_bar(2);
+        if (threadIdx.x == 0 && c > 0) request_tiles(c - 1, tM1, tM2);
         // ---- epilogue 3 ----
         // 16-bit copy of the new dS for the next (earlier) chunk
         if (c > 0) {
@@ -867,8 +878,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
                 else tmem_ld32(lane_addr + c0 + q4 * 32, av);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + kQ + sw_chunk(tid, q4 * 4 + j));
-                    const uint4 kv = *reinterpret_cast<const uint4*>(smem + kK + sw_chunk(tid, q4 * 4 + j));
+                    const uint4 qv = *reinterpret_cast<const uint4*>(smem + tQ + sw_chunk(tid, q4 * 4 + j));
+                    const uint4 kv = *reinterpret_cast<const uint4*>(smem + tK + sw_chunk(tid, q4 * 4 + j));
                     const uint32_t q4w[4] = {qv.x, qv.y, qv.z, qv.w};
                     const uint32_t k4w[4] = {kv.x, kv.y, kv.z, kv.w};
                     float o[8];
