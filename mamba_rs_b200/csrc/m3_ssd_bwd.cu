@@ -349,7 +349,7 @@ constexpr uint32_t kQ = 0, kK = 32768, kV = 65536, kDY = 81920, kSin = 98304, kD
 // 128-byte boundary (TMA destinations)
 constexpr uint32_t kStage = kVec + 12 * 128 * 4, kStageArr = 17 * 128;
 static_assert(kStage % 128 == 0 && kStageArr >= 129 * 16, "scalar staging");
-constexpr uint32_t kBar = kStage + 3 * kStageArr, kTmemSlot = kBar + 48, kSmem = kTmemSlot + 16;
+constexpr uint32_t kBar = kStage + 3 * kStageArr, kTmemSlot = kBar + 64, kSmem = kTmemSlot + 16;
 static_assert(kSmem <= 227 * 1024, "shared memory");
 constexpr uint32_t c0 = 0, c1 = 128, c2 = 256, c3 = 384, cDS = 448, kTmemCols = 512;
 constexpr uint32_t kStateTile = NS * HD * 2;  // bytes of one 16-bit state copy
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
     const uint32_t sbase = smem_u32(smem);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);  // 5: the chunk's tiles have landed (TMA)
+        for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);  // 5, 6: a chunk's tiles have landed (TMA)
         fence_barrier_init();
     }
     if (threadIdx.x < 32) {
@@ -476,35 +476,47 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
 
     // Tiles come by TMA (one thread; rows past T and columns past the head's width arrive as
     // zeros), the 16-bit state copy of a chunk by one contiguous bulk copy.
-    uint32_t tfph = 0;
-    auto load_qk = [&](uint32_t tile, const CUtensorMap* map, int t0) {
+    // barrier 5 for the backward pass and the even chunks of the state pass, 6 for its odd
+    // chunks (two requests are in flight there)
+    uint32_t tfph[2] = {0, 0};
+    auto load_qk = [&](uint32_t tile, const CUtensorMap* map, int t0, int bi) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) tma_load_4d(smem + tile + sub * kSwSub, map, &bars[5], 64 * sub, h, t0, b);
+        for (int sub = 0; sub < 2; ++sub)
+            tma_load_4d(smem + tile + sub * kSwSub, map, &bars[5 + bi], 64 * sub, h, t0, b);
     };
-    auto wait_tiles = [&]() {
-        ok = mbar_wait(&bars[5], tfph, p.status) && ok;
-        tfph ^= 1;
+    auto wait_tiles = [&](int bi) {
+        ok = mbar_wait(&bars[5 + bi], tfph[bi], p.status) && ok;
+        tfph[bi] ^= 1;
     };
 
     // ---------------- A. forward: 16-bit copies of the entering states ----------------
+    // K and V of chunk c + 1 are requested while chunk c is worked on; the pass needs few tiles,
+    // so odd chunks simply use the tiles the backward pass calls M1 and S_in.
+    auto request_kv = [&](int c) {  // one thread
+        const int t0 = c * CS;
+        mbar_expect_tx(&bars[5 + (c & 1)], 2 * kSwSub + kSwSub);
+        load_qk((c & 1) ? kM1 : kK, &p.tm_k, t0, c & 1);
+        tma_load_4d(smem + ((c & 1) ? kSin : kV), &p.tm_x, &bars[5 + (c & 1)], 0, h, t0, b);
+    };
+    if (threadIdx.x == 0 && nc > 1) {
+        issue_scalars_now(0);
+        request_kv(0);
+    }
     for (int c = 0; c < nc; ++c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
         const bool last = c + 1 == nc;
+        const uint32_t tKa = (c & 1) ? kM1 : kK, tVa = (c & 1) ? kSin : kV;
         float run = 0.0f, g = 0.0f, s = 0.0f;
         if (!last) {
-            issue_scalars(t0);
-            if (threadIdx.x == 0) {
-                mbar_expect_tx(&bars[5], 2 * kSwSub + kSwSub);
-                load_qk(kK, &p.tm_k, t0);
-                tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
-            }
+            if (threadIdx.x == 0 && c + 2 < nc) request_kv(c + 1);  // its tiles were last read by chunk c - 1
             load_scalars(t0, nv, run, g, s);
+            if (threadIdx.x == 0 && c + 2 < nc) issue_scalars_now(t0 + CS);  // the staging was read just above
             const float dA_end = dA[nv - 1];
             const float wt = tid < nv ? ex2((dA_end - run) * kLog2e) * s : 0.0f;
-            wait_tiles();
+            wait_tiles(c & 1);
 #pragma unroll
             for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(smem + kV + sw_chunk(tid, j));
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + tVa + sw_chunk(tid, j));
                 uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -541,7 +553,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
             const uint32_t idS = instr_desc(fmt, 1, 1, 64);
 #pragma unroll
             for (int k = 0; k < CS / 16; ++k)  // S^T[n][p] += sum_t K[t][n] (w V)[t][p]
-                mma(tmem + cDS, desc_sw_mn(sbase + kK, k), desc_sw_mn(sbase + kDY, k), idS, c > 0 || k > 0);
+                mma(tmem + cDS, desc_sw_mn(sbase + tKa, k), desc_sw_mn(sbase + kDY, k), idS, c > 0 || k > 0);
             commit(&bars[3]);
         }
         wait_bar(3);
@@ -563,8 +575,8 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         const int t0 = c * CS;
         issue_scalars_now(t0);
         mbar_expect_tx(&bars[5], 4 * kSwSub + 2 * kSwSub + (c > 0 ? kStateTile : 0));
-        load_qk(q_tile, &p.tm_q, t0);
-        load_qk(k_tile, &p.tm_k, t0);
+        load_qk(q_tile, &p.tm_q, t0, 0);
+        load_qk(k_tile, &p.tm_k, t0, 0);
         tma_load_4d(smem + kV, &p.tm_x, &bars[5], 0, h, t0, b);
         tma_load_4d(smem + kDY, &p.tm_dy, &bars[5], 0, h, t0, b);
         if (c > 0) bulk_load(smem + kSin, ws_st + static_cast<size_t>(c) * kStateTile, kStateTile, &bars[5]);
@@ -585,7 +597,7 @@ __global__ void __launch_bounds__(256) m3_ssd_bwd_tc_kernel(const __grid_constan
         const float w_t = lend_t * s_t;
         const long long qk_row = ((static_cast<long long>(b) * T + t) * nh + h) * nsv;
         const long long x_row = (static_cast<long long>(b) * T + t) * nh * hdv + h * hdv;
-        wait_tiles();
+        wait_tiles(0);
         // E o dY from the landed dY tile (own row, own half of the columns)
 #pragma unroll
         for (int j = half * (HD / 16); j < (half + 1) * (HD / 16); ++j) {
