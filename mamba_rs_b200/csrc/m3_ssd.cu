@@ -267,17 +267,18 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
             const float o = __shfl_up_sync(0xffffffffu, run, m);
             if (lane >= m) run += o;
         }
-        if (lane == 31) dA[warp] = run;  // slot reused below after the barrier
+        // warp totals in the 112 spare bytes behind the first staging array
+        float* wtot = reinterpret_cast<float*>(smem + kStage + 129 * 16);
+        if (lane == 31) wtot[warp] = run;
         gam[tid] = g;
         scl[tid] = s;
         if (GEN) dA[512 + tid] = dtr;
         __syncthreads();
-        float off = 0.0f;
-        for (int w = 0; w < warp; ++w) off += dA[w];
-        __syncthreads();
+        const float w0 = wtot[0], w1 = wtot[1], w2 = wtot[2];
+        const float off = (warp > 0 ? w0 : 0.0f) + (warp > 1 ? w1 : 0.0f) + (warp > 2 ? w2 : 0.0f);
         dA[tid] = run + off;
         dA[384 + tid] = (run + off) * kLog2e;
-        __syncthreads();
+        // (the barrier ahead of the first MMA group publishes these rows)
     };
 
 
