@@ -136,9 +136,11 @@ constexpr int CS = 128, HD = 64, NS = 128;
 // 16-bit copy of the new state for the next chunk's Y2; then f32 vectors, barriers.
 constexpr uint32_t kQ0 = 0, kK0 = 65536, kV0 = 131072, kQKStride = 32768, kVStride = 16384;
 constexpr uint32_t kM = 163840, kVw = 196608, kS = 196608;
-constexpr uint32_t kVec = 212992;  // f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128]
+// f32 dA[128], scale[128], gamma[128], dA*log2(e)[128], dt[128] per chunk, two sets: a chunk's
+// set is written while slower threads may still read the previous chunk's
+constexpr uint32_t kVec = 212992, kVecSet = 5 * 128;
 // K / Q generation: the angle entering the chunk, f64 [64]; this head's B / C biases [2][128]
-constexpr uint32_t kCarry = kVec + 5 * 128 * 4, kBias = kCarry + 64 * 8;
+constexpr uint32_t kCarry = kVec + 2 * kVecSet * 4, kBias = kCarry + 64 * 8;
 // per-row adt, dt, trap of a chunk (dt and trap with the row after it), two buffers,
 // filled by 4-byte asynchronous copies
 // [3][129 rows][4 heads] f32; a TMA destination has to start on a 128-byte boundary
@@ -182,7 +184,6 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
         mbar_init(bars + 4, 1);
         fence_barrier_init();
     }
-    float* dtv = vec + 512;
     double* carry = reinterpret_cast<double*>(smem + kCarry);
     float* bias_sm = reinterpret_cast<float*>(smem + kBias);
     if (GEN) {
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
         }
     };
     auto scalars = [&](int c, int st) {
-        float* dA = vec + st * 384;
+        float* dA = vec + st * kVecSet;
         float* scl = dA + 128;
         float* gam = dA + 256;
         if (p.sc_tma) {
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int row = lane + 32 * i;
-            const float dtr = row < nv ? dtv[row] : 0.0f;
+            const float dtr = row < nv ? vec[(c & 1) * kVecSet + 512 + row] : 0.0f;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 ang[i][q][0] = velr[i][q].x * dtr; ang[i][q][1] = velr[i][q].y * dtr;
@@ -428,14 +429,14 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
     for (int c = 0; c < nchunks; ++c) {
         const int t0 = c * CS, nv = min(CS, T - t0);
         const bool row_ok = tid < nv;
-        const float* dA = vec;
+        const float* dA = vec + (c & 1) * kVecSet;
         const float* scl = dA + 128;
         const float* gam = dA + 256;
         const uint32_t tQ = kQ0 + (c & 1) * kQKStride, tK = kK0 + (c & 1) * kQKStride, tV = kV0 + (c & 1) * kVStride;
         // ---- 1. copies of the next chunk's tiles into the other buffers (their last readers,
         //         the MMAs of chunk c - 1, have completed); per-row scalars; this chunk's tiles ----
         if (c + 1 < nchunks) issue_tiles(c + 1);
-        scalars(c, 0);
+        scalars(c, c & 1);
         ok = mbar_wait(&full[c & 1], (c >> 1) & 1, p.status) && ok;
         if (GEN) {
             gen_apply(c, c & 1);
@@ -600,10 +601,12 @@ __global__ void __launch_bounds__(256, 1) m3_ssd_fwd_tc_kernel(const __grid_cons
                 }
             }
         }
-        fence_before();
-        __syncthreads();
-        fence_after();
+        // no barrier here: the next chunk writes the other set of per-row vectors, and every tile,
+        // TMEM column and the state copy it touches is ordered by its own barriers
     }
+    fence_before();
+    __syncthreads();
+    fence_after();
     // last inputs of the window (kernels/mamba3_chunked.cu:289-330)
     if (T > 0) {
         const long long last = static_cast<long long>(b) * T + (T - 1);
