@@ -766,13 +766,22 @@ def main():
             for name in ("sscan_fwd_random_a", "sscan_bwd", "conv1d_fwd", "conv1d_bwd", "sscan_fwd_small_batch",
                          "decode_loop", "m3_ssd_fwd", "m3_ssd_fwd_fused_kq", "m3_ssd_bwd", "residual_rmsnorm_fwd",
                          "residual_rmsnorm_bwd", "softmax_xent", "adamw_step", "embedding_gather"):
-                r = measure_op(name, dev)
-                r.pop("op")
-                extra[name] = r
+                try:  # a failing extra must not take the headline line with it
+                    r = measure_op(name, dev)
+                    r.pop("op")
+                    extra[name] = r
+                except Exception as exc:
+                    extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                    torch.cuda.empty_cache()
         else:
-            c = collective_extra(dev, world, rank)
-            extra = {"gradient_allreduce": c}
-        extra.update(lm_extra(dev, world, rank))
+            try:
+                extra = {"gradient_allreduce": collective_extra(dev, world, rank)}
+            except Exception as exc:
+                extra = {"gradient_allreduce": {"error": f"{type(exc).__name__}: {exc}"[:300]}}
+        try:
+            extra.update(lm_extra(dev, world, rank))
+        except Exception as exc:
+            extra["lm"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         by = algorithmic_bytes(w)
