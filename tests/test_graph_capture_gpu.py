@@ -67,3 +67,58 @@ def test_forward_backward_conv_and_step_replay_bit_identically_from_a_graph(cuda
         for k, v in eager.items():
             np.testing.assert_array_equal(replayed[k], v, err_msg=k)
     mb.ffi.default_handle(0).check_status()
+
+
+def test_mamba3_tensor_core_kernels_replay_bit_identically_from_a_graph(cuda_dev):
+    """The Mamba-3 kernels take their TMA tensor maps as kernel parameters, built on the host
+    at launch: a captured launch keeps them, so a replay on the same buffers must reproduce the
+    eager results (forward, forward with K / Q built in the kernel, backward)."""
+    import torch
+
+    import mamba_rs_b200 as mb
+    from mamba_rs_b200 import synth
+    B, T, nh, ng, hd, N, na = 2, 300, 4, 1, 64, 128, 32
+    i = synth.m3_ssd_inputs(B, T, nh, hd, N, seed=4)
+    g = synth.m3_group_inputs(B, T, nh, ng, N, na, i["dt"], seed=4)
+    bf = torch.bfloat16
+    t = lambda a, d=None: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_dev).to(d or torch.float32)
+    x, K, Q = t(i["x"], bf), t(i["K"], bf), t(i["Q"], bf)
+    dt, trap, adt, Dh = t(i["dt"]), t(i["trap"]), t(i["adt"]), t(i["Dh"])
+    Bn, Cn, bb, cbias, vel = t(g["Bn"], bf), t(g["Cn"], bf), t(g["b_bias"]), t(g["c_bias"]), t(g["angle_vel"])
+    ang0 = t(g["angle_state"])
+    dy = torch.randn(B, T, nh * hd, device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(5)).to(bf)
+    y, y2 = torch.empty_like(x), torch.empty_like(x)
+    ssm = torch.zeros(B, nh, hd, N, device=cuda_dev)
+    ang = torch.empty_like(ang0)
+    dD = torch.zeros(nh, device=cuda_dev)
+    ws = torch.empty(mb.ffi.lib().mamba_b200_m3_ssd_bwd_workspace_bytes_for(2, B, T, nh, hd, N), dtype=torch.uint8,
+                     device=cuda_dev)
+    out = {}
+
+    def work():
+        ang.copy_(ang0)
+        dD.zero_()
+        mb.m3_ssd_fwd(x, K, Q, dt, trap, adt, Dh, ssm_state=ssm, y=y)
+        mb.ops.m3_ssd_fwd_fused_kq(x, Bn, Cn, bb, cbias, vel, dt, trap, adt, Dh, angle_state=ang, y=y2)
+        out.update(mb.m3_ssd_bwd(x, K, Q, dt, trap, adt, Dh, dy, dD=dD, workspace=ws))
+
+    def snapshot():
+        torch.cuda.synchronize()
+        keep = dict(out)
+        keep.update(y=y, y2=y2, ssm=ssm, ang=ang)
+        return {k: v.float().cpu().numpy().copy() for k, v in keep.items() if v is not None}
+
+    work()
+    eager = snapshot()
+    side = torch.cuda.Stream(device=cuda_dev)
+    side.wait_stream(torch.cuda.current_stream(cuda_dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        work()
+    for _ in range(2):
+        y.zero_(); y2.zero_()
+        graph.replay()
+        replayed = snapshot()
+        for k, v in eager.items():
+            np.testing.assert_array_equal(replayed[k], v, err_msg=k)
+    mb.ffi.default_handle(0).check_status()
